@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 8
+#define B200_ABI_VERSION 9
 
 enum {
   B200_OK = 0,
@@ -280,6 +280,71 @@ int b200_allreduce_rmsnorm_nvls(const void* mc_buf, void* const* host_peer_flags
 int b200_tp_argmax_merge(const void* const* host_peer_vals, const void* const* host_peer_idxs,
                          void* const* host_peer_flags, uint32_t* epoch, int rank, int world, int64_t* out_ids, int B,
                          void* stream);
+
+/* ---------------------------------------------------------------- hybrid decoders (state-space + windowed attention + MoE)
+ * Kernels for decoders that mix state-space layers, sliding-window attention with a softmax sink, Dynamic-Tanh norms and
+ * a mixture-of-experts feed-forward.  The residual stream, norms, softmax, router and recurrences are fp32; `*_dtype`
+ * arguments (B200_BF16 or B200_F32) name the type of GEMM operands, weights and KV pools.
+ * A step is a RAGGED batch: B sequences, sequence s brings tokens [seq_start[s], seq_start[s+1]) of the flattened batch,
+ * continues at position seq_pos0[s] and owns state slot seq_slot[s]; tok_seq[t] is the sequence of token t.  A sequence
+ * with seq_pos0 == 0 starts from zero state whatever its slot held. */
+
+/* out[t][:] = table[tokens[t]][:] * scale (fp32 residual stream) */
+int b200_embed_scale(const int32_t* tokens, const void* table, int table_dtype, float* out, int T, int W, int V, float scale,
+                     void* stream);
+/* Dynamic Tanh: out[i] = gain[i] * tanh(a * x[i]) + shift[i] (a: one scalar per norm); x fp32 [T][W], gain `w` / shift `b` fp32 [W],
+ * out in out_dtype */
+int b200_dyt_norm(const float* x, const float* w, const float* b, float alpha, void* out, int out_dtype, int T, int W,
+                  void* stream);
+/* x[t] += dyt1(sum_{c < nsum} y[t * nsum + c] + y2[t]);  out2[t] = dyt2(x[t]) when out2 != NULL.  y fp32 [T * nsum][W],
+ * y2 fp32 [T][W] or NULL. */
+int b200_dyt_residual(float* x, const float* y, int nsum, const float* y2, const float* w1, const float* b1, float alpha1,
+                      const float* w2, const float* b2, float alpha2, void* out2, int out_dtype, int T, int W, void* stream);
+/* r = y * silu(z) first, then each of the `groups` equal slices r_k of a row becomes r_k * rsqrt(mean(r_k^2) + eps), times w.
+ * y fp32 [T][inner]; z fp32 rows of pitch ldz. */
+int b200_gated_group_rmsnorm(const float* y, const float* z, int ldz, const float* w, void* out, int out_dtype, int T,
+                             int inner, int groups, float eps, void* stream);
+/* gate_up fp32 [T][2 ff] (gate first): a = min(gate, L), b = max(-L, min(up, L)), out = (b + 1) * a / (1 + exp(-1.702 a)) */
+int b200_clamped_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, float limit, void* stream);
+/* Causal depthwise convolution + SiLU over columns [col0, col0 + C) of `in` (fp32, pitch ld); conv_w fp32 [C][taps] with
+ * the LAST tap on the current token; state fp32 [slots][taps - 1][C] holds each sequence's last inputs and is updated. */
+int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
+                          const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                          void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
+/* Selective state-space scan: xbc [T][C] = [x: H*P | B: G*N | C: G*N] (x_dtype); dt_raw = dt_in[t][dt_col0 + h] (fp32);
+ * dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x.
+ * state fp32 [slots][H][N][P], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256. */
+int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
+                  const float* dt_bias, const float* D, float* state, const int32_t* seq_start, const int32_t* seq_slot,
+                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, void* stream);
+/* Scatter keys [G][D] (columns k_col0..) and values [G][Dv] (columns v_col0..) of the fp32 rows `qkv` into the pools
+ * K [num_blocks][G][block_size][D], V [num_blocks][G][block_size][Dv] by slot (slot < 0: skipped).
+ * mode 0: plain; 1: also keep the unmixed values in v_first fp32 [T][G*Dv]; 2: cache v + lambda * (v_first - v) instead of v. */
+int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* v_first, float lambda, int mode, void* k_pool,
+                       void* v_pool, int kv_dtype, const int64_t* slot_mapping, int T, int G, int D, int Dv, int block_size,
+                       void* stream);
+/* Sliding-window attention with a per-head sink logit in the softmax denominator, no positional rotation.
+ * q fp32 rows (pitch ldq, head h at column h * D); token t is position tok_pos[t] of the sequence whose block-table row is
+ * tok_row[t] and sees keys j with 0 <= pos - j < window, all already in the pools.  out [T][H][Dv] in kv_dtype. */
+int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
+                       int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
+                       int window, void* out, int T, int H, int G, int D, int Dv, int block_size, void* stream);
+/* Router: fp32 logits W_router h, sigmoid scores, the `top` largest (ties to the lower index); weights = chosen scores. */
+int b200_moe_router(const void* h, const void* w_router, int dtype, int32_t* topk_idx, float* topk_weight, int T, int W, int E,
+                    int top, void* stream);
+/* rows per expert tile of b200_moe_align / b200_grouped_linear */
+int b200_moe_tile_rows(void);
+/* Sort the npairs (token, choice) pairs by expert into tiles: sorted_ids [cap] (pair id or -1), tile_expert [max_tiles],
+ * *num_tiles.  Needs max_tiles >= ceil(npairs / tile_rows) + E and cap >= max_tiles * tile_rows. */
+int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
+                   int32_t* num_tiles, void* stream);
+/* out = A W_e^T, fp32 accumulation.  Dense (sorted_ids NULL): rows 0..M-1, one weight.  Grouped: row tile i belongs to
+ * expert tile_expert[i]; row r of the tile list is pair sorted_ids[r]; its A row is pair / gather_div (gather_div > 0,
+ * scaled by row_scale[pair]) or r itself; its out row is the pair id (scatter) or r.  glu: w_e = [gate; up] of N rows each
+ * and out (dtype) = clamped GLU; else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit). */
+int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
+                        int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, void* stream);
 
 #ifdef __cplusplus
 }

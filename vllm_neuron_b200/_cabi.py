@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200_paged.so")
 
 OK = 0
-ABI_VERSION = 8
+ABI_VERSION = 9
 BF16, FP8_E4M3, INT8, F32 = 0, 1, 2, 3
 
 _p = C.c_void_p
@@ -67,6 +67,20 @@ SIGNATURES = {
     "b200_gemm_silu_mul_quant": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "b200_tp_argmax_merge": (_i, [_p, _p, _p, _p, _i, _i, _p, _i, _p]),
     "b200_allreduce_rmsnorm_nvls": (_i, [_p, _p, _p, _i, _i, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p]),
+    # hybrid decoders: Dynamic-Tanh norms, state-space scan, windowed attention with a sink, mixture of experts
+    "b200_embed_scale": (_i, [_p, _p, _i, _p, _i, _i, _i, _f, _p]),
+    "b200_dyt_norm": (_i, [_p, _p, _p, _f, _p, _i, _i, _i, _p]),
+    "b200_dyt_residual": (_i, [_p, _p, _i, _p, _p, _p, _f, _p, _p, _f, _p, _i, _i, _i, _p]),
+    "b200_gated_group_rmsnorm": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _f, _p]),
+    "b200_clamped_glu": (_i, [_p, _p, _i, _i, _i, _f, _p]),
+    "b200_causal_conv_silu": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_ssd_scan": (_i, [_p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_kv_write_vmix": (_i, [_p, _i, _i, _i, _p, _f, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_router": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _p]),
+    "b200_moe_tile_rows": (_i, []),
+    "b200_moe_align": (_i, [_p, _i, _i, _p, _i, _p, _i, _p, _p]),
+    "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _f, _p]),
 }
 
 _lib = None

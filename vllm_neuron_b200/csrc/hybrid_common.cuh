@@ -1,0 +1,42 @@
+// Helpers shared by the hybrid-decoder kernels (Dynamic-Tanh norms, state-space scan, sliding-window attention with a
+// softmax sink, mixture of experts).  These kernels keep the residual stream, every norm, softmax, router and recurrence
+// in fp32; the element type T (bf16 or float) is the type of GEMM operands, KV pools and weights: bf16 when the model is
+// served in bf16, float when it runs entirely in 32-bit.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p, int64_t i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, int64_t i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+
+template <typename T>
+__device__ __forceinline__ void stf(T* p, int64_t i, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, int64_t i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// exact-exponential SiLU (the fp32 serving mode compares at 1e-5; common.cuh's silu_f32 is the fast-path variant)
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// element-type dispatch: `dt` is B200_BF16 or B200_F32
+#define B200_DISPATCH_ELEM(dt, T, ...)                                        \
+  do {                                                                        \
+    if ((dt) == B200_BF16) {                                                  \
+      using T = __nv_bfloat16;                                                \
+      __VA_ARGS__;                                                            \
+    } else if ((dt) == B200_F32) {                                            \
+      using T = float;                                                        \
+      __VA_ARGS__;                                                            \
+    } else {                                                                  \
+      ::b200::set_last_error("element type %d is neither bf16 nor f32", dt);  \
+      return B200_ERR_INVALID_ARG;                                            \
+    }                                                                         \
+  } while (0)
+
+}  // namespace b200

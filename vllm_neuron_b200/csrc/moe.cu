@@ -1,0 +1,254 @@
+// Mixture-of-experts feed-forward over a token batch, and the generic grouped / dense linear kernel it is built on.
+//   * moe_router: logits = W_router h in fp32, score = sigmoid(logit); the `top` largest scores are chosen (ties go to the
+//     lower expert index) and the chosen SCORES are the routing weights (no renormalisation);
+//   * moe_align: counting sort of the (token, choice) pairs by expert into row tiles of MOE_BM, each tile owned by one
+//     expert (ragged tails padded with -1), so the expert GEMMs run as one launch without the host knowing the counts;
+//   * grouped_linear: out = A W_e^T with fp32 accumulation over K in ascending order (the result of a row does not depend
+//     on what else is in the batch).  A rows can be gathered per pair and scaled by the pair's routing weight (the
+//     scaling happens on the way INTO the expert, ahead of its nonlinearity), and the epilogue is either a plain fp32 store (optionally scattered back to
+//     pair order) or the clamped gated-linear unit over a [gate; up] weight.
+// With one expert, no gather and no scatter the same kernel is the dense linear for operand types or shapes the
+// tensor-core GEMM does not take (fp32 operands, K not a multiple of 8).
+#include "hybrid_common.cuh"
+
+namespace b200 {
+
+constexpr int MOE_BM = 32;
+constexpr int GL_BN = 64;
+constexpr int GL_BK = 16;
+constexpr int GL_THREADS = 256;
+
+template <typename T>
+__global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__ wr, int W, int E, int top,
+                                  int32_t* __restrict__ idx, float* __restrict__ wt, int ntok) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ float zs_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= ntok) return;
+  float* z = zs_all + warp * E;
+  const T* hr = h + (int64_t)t * W;
+  for (int e = 0; e < E; ++e) {
+    const T* w = wr + (int64_t)e * W;
+    float acc = 0.f;
+    for (int i = lane; i < W; i += 32) acc += ldf(hr, i) * ldf(w, i);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < bi)) {
+        best = v;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      idx[(int64_t)t * top + c] = bi;
+      wt[(int64_t)t * top + c] = 1.0f / (1.0f + expf(-best));
+      z[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// single CTA: counts -> padded offsets -> tile owners -> scatter of pair ids
+__global__ void moe_align_kernel(const int32_t* __restrict__ idx, int npairs, int E, int32_t* __restrict__ sorted_ids, int cap,
+                                 int32_t* __restrict__ tile_expert, int max_tiles, int32_t* __restrict__ num_tiles) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ int32_t sm[];
+  int32_t* counts = sm;
+  int32_t* offs = sm + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted_ids[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = o;
+      const int tiles = (counts[e] + MOE_BM - 1) / MOE_BM;
+      for (int k = 0; k < tiles && nt < max_tiles; ++k) tile_expert[nt++] = e;
+      o += tiles * MOE_BM;
+    }
+    *num_tiles = nt;
+  }
+  __syncthreads();
+  // order inside an expert's rows follows the atomics; every row is computed on its own, so results do not depend on it
+  for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+    const int p = atomicAdd(&offs[idx[i]], 1);
+    sorted_ids[p] = i;
+  }
+}
+
+enum { GL_EPI_STORE = 0, GL_EPI_GLU = 1 };
+
+// Row tile `blockIdx.x` (MOE_BM rows), column tile `blockIdx.y` (GL_BN outputs).  256 threads, each 2 rows x 4 columns.
+template <typename T, int EPI>
+__global__ void __launch_bounds__(GL_THREADS)
+    grouped_linear_kernel(const T* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
+                          const float* __restrict__ row_scale, const T* __restrict__ w, int64_t w_stride,
+                          const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles, int M, int N, int K,
+                          void* __restrict__ out, int ldo, int scatter, float limit) {
+  griddep_launch();
+  griddep_wait();
+  constexpr int NW = EPI == GL_EPI_GLU ? 2 : 1;
+  __shared__ float As[GL_BK][MOE_BM + 1];
+  __shared__ float Ws[NW][GL_BK][GL_BN + 1];
+  __shared__ int32_t rid[MOE_BM];     // source row in `a` (or -1)
+  __shared__ int32_t oid[MOE_BM];     // destination row in `out` (or -1)
+  __shared__ float rsc[MOE_BM];
+  const int tile = blockIdx.x;
+  if (num_tiles && tile >= *num_tiles) return;
+  const int e = tile_expert ? tile_expert[tile] : 0;
+  const T* we = w + (int64_t)e * w_stride;
+  const int n0 = blockIdx.y * GL_BN;
+  if (threadIdx.x < MOE_BM) {
+    const int r = tile * MOE_BM + threadIdx.x;
+    int src = -1, dst = -1;
+    float sc = 1.0f;
+    if (sorted_ids) {
+      const int id = sorted_ids[r];
+      if (id >= 0) {
+        src = gather_div > 0 ? id / gather_div : r;
+        dst = scatter ? id : r;
+        if (row_scale) sc = row_scale[id];
+      }
+    } else if (r < M) {
+      src = dst = r;
+    }
+    rid[threadIdx.x] = src;
+    oid[threadIdx.x] = dst;
+    rsc[threadIdx.x] = sc;
+  }
+  __syncthreads();
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;  // rows 2 ty, 2 ty + 1; columns 4 tx .. 4 tx + 3
+  float acc[NW][2][4];
+#pragma unroll
+  for (int x = 0; x < NW; ++x)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[x][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += GL_BK) {
+    for (int i = threadIdx.x; i < MOE_BM * GL_BK; i += GL_THREADS) {
+      const int r = i / GL_BK, k = i % GL_BK;
+      float v = 0.f;
+      if (rid[r] >= 0 && k0 + k < K) v = ldf(a, (int64_t)rid[r] * lda + k0 + k) * rsc[r];
+      As[k][r] = v;
+    }
+    for (int i = threadIdx.x; i < NW * GL_BN * GL_BK; i += GL_THREADS) {
+      const int x = i / (GL_BN * GL_BK), rem = i % (GL_BN * GL_BK);
+      const int n = rem / GL_BK, k = rem % GL_BK;
+      float v = 0.f;
+      if (n0 + n < N && k0 + k < K) v = ldf(we, ((int64_t)x * N + n0 + n) * K + k0 + k);
+      Ws[x][k][n] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GL_BK; ++k) {
+      const float a0 = As[k][2 * ty], a1 = As[k][2 * ty + 1];
+#pragma unroll
+      for (int x = 0; x < NW; ++x)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float wv = Ws[x][k][4 * tx + j];
+          acc[x][0][j] += a0 * wv;
+          acc[x][1][j] += a1 * wv;
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int dst = oid[2 * ty + i];
+    if (dst < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + 4 * tx + j;
+      if (n >= N) continue;
+      if (EPI == GL_EPI_GLU) {
+        const float g = fminf(acc[0][i][j], limit);
+        const float u = fminf(fmaxf(acc[NW - 1][i][j], -limit), limit);
+        stf((T*)out, (int64_t)dst * ldo + n, g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+      } else {
+        ((float*)out)[(int64_t)dst * ldo + n] = acc[0][i][j];
+      }
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_moe_router(const void* h, const void* w_router, int dtype, int32_t* topk_idx, float* topk_weight, int T, int W, int E,
+                    int top, void* stream) {
+  B200_REQUIRE(h && w_router && topk_idx && topk_weight, "moe_router: null pointer");
+  B200_REQUIRE(E >= 1 && E <= 4096 && top >= 1 && top <= E, "moe_router: top %d of %d experts", top, E);
+  if (T <= 0) return B200_OK;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * 4;
+  B200_DISPATCH_ELEM(dtype, ET, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(moe_router_kernel<ET>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_OK(launch_kernel(moe_router_kernel<ET>, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, (cudaStream_t)stream,
+                               (const ET*)h, (const ET*)w_router, W, E, top, topk_idx, topk_weight, T));
+  });
+  return B200_OK;
+}
+
+int b200_moe_tile_rows(void) { return MOE_BM; }
+
+int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
+                   int32_t* num_tiles, void* stream) {
+  B200_REQUIRE(topk_idx && sorted_ids && tile_expert && num_tiles, "moe_align: null pointer");
+  B200_REQUIRE(E >= 1 && E <= 4096, "moe_align: %d experts", E);
+  B200_REQUIRE(max_tiles >= (npairs + MOE_BM - 1) / MOE_BM + E && cap >= max_tiles * MOE_BM,
+               "moe_align: %d tiles / %d rows cannot hold %d pairs of %d experts", max_tiles, cap, npairs, E);
+  if (npairs <= 0) return B200_OK;
+  B200_CUDA_OK(launch_kernel(moe_align_kernel, dim3(1), dim3(1024), (size_t)2 * E * 4, (cudaStream_t)stream, topk_idx, npairs, E,
+                             sorted_ids, cap, tile_expert, max_tiles, num_tiles));
+  return B200_OK;
+}
+
+int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
+                        int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, void* stream) {
+  B200_REQUIRE(a && w && out, "grouped_linear: null pointer");
+  B200_REQUIRE(N > 0 && K > 0 && row_tiles >= 0, "grouped_linear: bad shape N=%d K=%d", N, K);
+  B200_REQUIRE(sorted_ids || (!tile_expert && !num_tiles && !row_scale), "grouped_linear: expert tiles need the sorted pair list");
+  if (row_tiles == 0) return B200_OK;
+  dim3 grid(row_tiles, (N + GL_BN - 1) / GL_BN);
+  cudaStream_t st = (cudaStream_t)stream;
+  B200_DISPATCH_ELEM(dtype, ET, {
+    if (glu)
+      B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_GLU>, grid, dim3(GL_THREADS), 0, st, (const ET*)a, lda, sorted_ids,
+                                 gather_div, row_scale, (const ET*)w, w_expert_stride, tile_expert, num_tiles, M, N, K, out, ldo,
+                                 scatter, limit));
+    else
+      B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_STORE>, grid, dim3(GL_THREADS), 0, st, (const ET*)a, lda,
+                                 sorted_ids, gather_div, row_scale, (const ET*)w, w_expert_stride, tile_expert, num_tiles, M, N, K,
+                                 out, ldo, scatter, limit));
+  });
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,208 @@
+// State-space (Mamba-2 style) mixer kernels over a ragged batch: every sequence of the step brings n >= 1 new tokens that
+// continue from the state its slot holds (a prompt portion and a single decoded token are the same code).
+//   * causal depthwise convolution + SiLU over the channels [x | B | C]; the last (taps - 1) inputs of a sequence are
+//     part of its state (fp32, [slots][taps - 1][channels], oldest first);
+//   * the selective scan  S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T,  y_t = S_t^T C_t + D x_t  with
+//     dt_t = softplus(dt_raw + dt_bias), S in fp32 ([slots][heads][N][P]) and every term of the recurrence in fp32.
+// A sequence whose first new token is position 0 starts from zero state whatever its slot held before, so slots can be
+// handed to new requests without clearing them.
+#include "hybrid_common.cuh"
+
+namespace b200 {
+
+constexpr int CONV_MAX_TAPS = 16;
+
+// one thread per (token, channel)
+template <typename OT>
+__global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cw,
+                                        const float* __restrict__ cb, const float* __restrict__ state,
+                                        const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_start,
+                                        const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos0,
+                                        OT* __restrict__ out, int C, int taps) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s = tok_seq[t];
+  const int i = t - seq_start[s];  // index inside this step's portion
+  const bool has_state = seq_pos0[s] > 0;
+  const float* st = state + (int64_t)seq_slot[s] * (taps - 1) * C;
+  float acc = cb[c];
+  for (int j = 0; j < taps; ++j) {
+    const int src = i - (taps - 1 - j);  // portion index of the input under tap j (last tap = current token)
+    float v;
+    if (src >= 0)
+      v = in[(int64_t)(t - (taps - 1 - j)) * ld + col0 + c];
+    else if (has_state)
+      v = st[(int64_t)(src + taps - 1) * C + c];
+    else
+      v = 0.f;
+    acc += v * cw[(int64_t)c * taps + j];
+  }
+  stf(out, (int64_t)t * C + c, silu_f(acc));
+}
+
+// new state = the last (taps - 1) inputs of [old state | this step's inputs]; one thread per (sequence, channel) reads
+// everything it needs before it writes, so the update is in place.  Runs after causal_conv_silu_kernel on the stream.
+__global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, int col0, float* __restrict__ state,
+                                         const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                                         const int32_t* __restrict__ seq_pos0, int C, int taps) {
+  griddep_launch();
+  griddep_wait();
+  const int s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int t0 = seq_start[s], n = seq_start[s + 1] - t0, pos0 = seq_pos0[s];
+  float* st = state + (int64_t)seq_slot[s] * (taps - 1) * C;
+  float keep[CONV_MAX_TAPS];
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; ++k) {
+    if (k < taps - 1) {
+      const int i = n - (taps - 1) + k;  // portion index of what slot k must hold afterwards
+      float v = 0.f;
+      if (i >= 0)
+        v = in[(int64_t)(t0 + i) * ld + col0 + c];
+      else if (pos0 > 0)
+        v = st[(int64_t)(i + taps - 1) * C + c];
+      keep[k] = v;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < CONV_MAX_TAPS - 1; ++k)
+    if (k < taps - 1) st[(int64_t)k * C + c] = keep[k];
+}
+
+// Selective scan.  CTA = (32 value columns p of one head) x (8 slices of the state dimension); thread (p, s) keeps
+// S[n][p] for n = s, s + 8, ... (NPT of them) in registers across the tokens of its sequence; y is reduced over the 8
+// slices with shuffles.  The next token's operands are fetched while the current one is applied.
+constexpr int SCAN_PCOLS = 32;
+constexpr int SCAN_SLICES = 8;
+
+template <typename XT, int NPT>
+__global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
+    ssd_scan_kernel(const XT* __restrict__ xbc, int C, const float* __restrict__ dt_in, int ld_dt, int dt_col0,
+                    const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
+                    float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                    const int32_t* __restrict__ seq_pos0, float* __restrict__ y, int H, int P, int N, int G) {
+  griddep_launch();
+  griddep_wait();
+  const int h = blockIdx.y, sq = blockIdx.z;
+  const int s = threadIdx.x % SCAN_SLICES;
+  const int p = blockIdx.x * SCAN_PCOLS + threadIdx.x / SCAN_SLICES;
+  const bool pv = p < P;
+  const int pc = pv ? p : P - 1;
+  const int g = h / (H / G);
+  const int inner = H * P;
+  const int t0 = seq_start[sq], t1 = seq_start[sq + 1];
+  float* S0 = state + (((int64_t)seq_slot[sq] * H + h) * N) * P + pc;
+  float S[NPT];
+  const bool cont = seq_pos0[sq] > 0;
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = s + i * SCAN_SLICES;
+    S[i] = (cont && n < N) ? S0[(int64_t)n * P] : 0.f;
+  }
+  const float negA = -expf(A_log[h]), bias = dt_bias[h], dsk = Dskip[h];
+  const int64_t xcol = (int64_t)h * P + pc, bcol = (int64_t)inner + (int64_t)g * N, ccol = bcol + (int64_t)G * N;
+
+  float Bn[NPT], Cn[NPT], xv, dtr;
+  auto fetch = [&](int t) {
+    const XT* row = xbc + (int64_t)t * C;
+    xv = ldf(row, xcol);
+    dtr = dt_in[(int64_t)t * ld_dt + dt_col0 + h];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = s + i * SCAN_SLICES;
+      Bn[i] = n < N ? ldf(row, bcol + n) : 0.f;
+      Cn[i] = n < N ? ldf(row, ccol + n) : 0.f;
+    }
+  };
+  if (t0 < t1) fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    float Bc[NPT], Cc[NPT];
+    const float xc = xv, dtc = dtr;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      Bc[i] = Bn[i];
+      Cc[i] = Cn[i];
+    }
+    if (t + 1 < t1) fetch(t + 1);
+    const float z = dtc + bias;
+    const float dt = z > 20.f ? z : log1pf(expf(z));  // softplus, no clamp on the step size
+    const float a = expf(negA * dt);
+    const float dx = dt * xc;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      S[i] = a * S[i] + Bc[i] * dx;
+      acc += S[i] * Cc[i];
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (s == 0 && pv) y[(int64_t)t * inner + xcol] = acc + dsk * xc;
+  }
+  if (pv) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = s + i * SCAN_SLICES;
+      if (n < N) S0[(int64_t)n * P] = S[i];
+    }
+  }
+}
+
+template <typename XT, int NPT>
+static int launch_scan(const void* xbc, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
+                       const float* dt_bias, const float* Dskip, float* state, const int32_t* seq_start, const int32_t* seq_slot,
+                       const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, cudaStream_t stream) {
+  dim3 grid((P + SCAN_PCOLS - 1) / SCAN_PCOLS, H, B);
+  B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT>, grid, dim3(SCAN_PCOLS * SCAN_SLICES), 0, stream, (const XT*)xbc, C, dt_in,
+                             ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y, H, P, N, G));
+  return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
+                          const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                          void* out, int out_dtype, int T, int B, int C, int taps, void* stream) {
+  B200_REQUIRE(in && conv_w && conv_b && state && tok_seq && seq_start && seq_slot && seq_pos0 && out, "causal_conv_silu: null pointer");
+  B200_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv_silu: %d taps (1..%d supported)", taps, CONV_MAX_TAPS);
+  if (T <= 0 || B <= 0) return B200_OK;
+  const int th = 128;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(causal_conv_silu_kernel<OT>, dim3((C + th - 1) / th, T), dim3(th), 0,
+                                                (cudaStream_t)stream, in, ld, col0, conv_w, conv_b, (const float*)state, tok_seq,
+                                                seq_start, seq_slot, seq_pos0, (OT*)out, C, taps)));
+  if (taps > 1)
+    B200_CUDA_OK(launch_kernel(conv_state_update_kernel, dim3((C + th - 1) / th, B), dim3(th), 0, (cudaStream_t)stream, in, ld,
+                               col0, state, seq_start, seq_slot, seq_pos0, C, taps));
+  return B200_OK;
+}
+
+int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
+                  const float* dt_bias, const float* D, float* state, const int32_t* seq_start, const int32_t* seq_slot,
+                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, void* stream) {
+  B200_REQUIRE(xbc && dt_in && A_log && dt_bias && D && state && seq_start && seq_slot && seq_pos0 && y, "ssd_scan: null pointer");
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "ssd_scan: %d heads do not split into %d groups", H, G);
+  B200_REQUIRE(N >= 1 && N <= 256, "ssd_scan: state size %d (1..256 supported)", N);
+  B200_REQUIRE(C == H * P + 2 * G * N, "ssd_scan: %d channels != heads * vdim + 2 * groups * state", C);
+  if (B <= 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+#define SCAN_ARGS xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, D, state, seq_start, seq_slot, seq_pos0, y, B, H, P, N, G, st
+  B200_DISPATCH_ELEM(x_dtype, XT, {
+    if (N <= 32) return launch_scan<XT, 4>(SCAN_ARGS);
+    if (N <= 64) return launch_scan<XT, 8>(SCAN_ARGS);
+    if (N <= 128) return launch_scan<XT, 16>(SCAN_ARGS);
+    return launch_scan<XT, 32>(SCAN_ARGS);
+  });
+#undef SCAN_ARGS
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,427 @@
+"""Hybrid decoders: state-space and sliding-window-attention mixers with Dynamic-Tanh norms and a mixture-of-experts
+feed-forward, served from a configuration that lists the layers one by one (the "Pumopel" design).
+
+A layer is   x += N1b(mixer(N1(x)));  x += N2b(ff(N2(x)))   with N(x) = gain * tanh(a x) + shift (elementwise).  Mixers:
+  * 'mamba2'    -- in-projection -> [z | x | B | C | dt]; causal depthwise convolution + SiLU over [x | B | C]; selective scan
+                   S <- exp(-exp(A_log) d) S + d B x^T, y = S^T C + D x with step size d = softplus(raw + dt_bias), per head;
+                   y * silu(z), RMS norm in `norm_groups` equal parts, out-projection.  State per sequence: S (fp32) and the last
+                   taps - 1 convolution inputs.
+  * 'attention' -- q / k / v projections without bias or rotation, GQA, key width `dim` != value width `vdim`, sliding window
+                   (query i attends keys i - mask.size < j <= i), a per-head sink logit that only enlarges the softmax
+                   denominator, and value mixing: every v_mix layer after the first caches v + lambda (v_first - v), v_first being
+                   the first such layer's value of the same token.
+Feed-forward: sigmoid router, `top` experts by score, weights = scores (not renormalised) applied to the expert's INPUT,
+experts down((b + 1) a / (1 + exp(-1.702 a))) with a = min(gate(h), L), b = clip(up(h), -L, L), plus an always-on shared
+expert.  Every size and constant above is read from the configuration.
+
+The step is ONE ragged batch (`StepMeta`): portions of prompts and single decoded tokens run through the same kernels, each
+sequence continuing from its KV pages (block table row) and its state slot.  fp32 everywhere the design asks for it
+(residual stream, norms, softmax, router, recurrence); GEMM operands, weights and KV pools are bf16, or fp32 when the model is
+built with dtype=torch.float32 (then no tensor-core GEMM is used at all).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+
+import torch
+
+from . import ops
+
+ARCHITECTURE = "Pumopel"
+_NO_WINDOW = 1 << 30
+
+
+# ------------------------------------------------------------------------------------------------ configuration
+@dataclass
+class SsmSpec:
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def channels(self) -> int:  # what the convolution sees: [x | B | C]
+        return self.inner + 2 * self.groups * self.state
+
+    @property
+    def proj(self) -> int:  # rows of the in-projection: [z | x | B | C | dt]
+        return self.inner + self.channels + self.heads
+
+
+@dataclass
+class AttnSpec:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int = _NO_WINDOW
+    v_mix: bool = False
+
+
+@dataclass
+class MoeSpec:
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+
+@dataclass
+class LayerSpec:
+    kind: str  # 'mamba2' | 'attention'
+    mixer: object
+    mlp: MoeSpec | None
+
+
+@dataclass
+class HybridConfig:
+    vocab: int
+    width: int
+    eps: float
+    embed_scale: float
+    layers: list = field(default_factory=list)
+    name: str = ARCHITECTURE
+
+    @staticmethod
+    def from_dict(d: dict) -> "HybridConfig":
+        layers = []
+        for L in d["layers"]:
+            m = L["mixer"]
+            if L["type"] == "mamba2":
+                mixer = SsmSpec(int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["conv"]),
+                                int(m.get("norm_groups", 1)))
+                if mixer.heads % mixer.groups or mixer.inner % mixer.norm_groups:
+                    raise ValueError(f"mamba2 layer: heads {mixer.heads} / groups {mixer.groups} / norm_groups {mixer.norm_groups}")
+            elif L["type"] == "attention":
+                mask = m.get("mask") or {}
+                mixer = AttnSpec(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), float(m["scale"]),
+                                 int(mask.get("size", _NO_WINDOW)), bool(m.get("v_mix", False)))
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f"attention layer: {mixer.heads} query heads over {mixer.kv_heads} kv heads")
+            else:
+                raise ValueError(f"unknown layer type {L['type']!r}")
+            f = L.get("mlp")
+            mlp = None
+            if f:
+                if f.get("kind", "moe") != "moe":
+                    raise ValueError(f"unknown feed-forward kind {f.get('kind')!r}")
+                sh = f.get("shared") or {}
+                mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
+                              float(f["expert"]["limit"]), int(sh.get("ff", 0)), float(sh.get("limit", 0.0)))
+            layers.append(LayerSpec(L["type"], mixer, mlp))
+        return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(d["embedding"]["scale"]), layers,
+                            d.get("architecture", ARCHITECTURE))
+
+    @staticmethod
+    def from_pretrained(path: str) -> "HybridConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            return HybridConfig.from_dict(json.load(f))
+
+    def to_dict(self) -> dict:
+        """The configuration in its file form (what from_dict reads)."""
+        out = {"architecture": self.name, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
+               "embedding": {"scale": self.embed_scale}, "layers": []}
+        for L in self.layers:
+            m = L.mixer
+            if L.kind == "mamba2":
+                mixer = {"heads": m.heads, "vdim": m.vdim, "state": m.state, "groups": m.groups, "conv": m.conv,
+                         "norm_groups": m.norm_groups}
+            else:
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+                         "v_mix": m.v_mix}
+                if m.window != _NO_WINDOW:
+                    mixer["mask"] = {"size": m.window}
+            f = None
+            if L.mlp:
+                f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top},
+                     "expert": {"ff": L.mlp.ff, "limit": L.mlp.limit},
+                     "shared": {"ff": L.mlp.shared_ff, "limit": L.mlp.shared_limit} if L.mlp.shared_ff else None}
+            out["layers"].append({"type": L.kind, "mixer": mixer, "mlp": f})
+        return out
+
+
+def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
+    """Checkpoint tensor name -> shape (a linear layer's matrix has one row per output)."""
+    W = cfg.width
+    s: dict[str, tuple] = {"embed": (cfg.vocab, W), "head": (cfg.vocab, W)}
+
+    def norm(n):
+        s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
+
+    norm("final.norm")
+    for i, L in enumerate(cfg.layers):
+        p = f"l{i}."
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ()):
+            norm(p + n)
+        m = L.mixer
+        if L.kind == "mamba2":
+            s.update({p + "mix.in": (m.proj, W), p + "mix.conv": (m.channels, m.conv), p + "mix.conv.b": (m.channels,),
+                      p + "mix.dt_bias": (m.heads,), p + "mix.A_log": (m.heads,), p + "mix.D": (m.heads,),
+                      p + "mix.norm": (m.inner,), p + "mix.o": (W, m.inner)})
+        else:
+            s.update({p + "mix.q": (m.heads * m.dim, W), p + "mix.k": (m.kv_heads * m.dim, W), p + "mix.v": (m.kv_heads * m.vdim, W),
+                      p + "mix.sink": (m.heads,), p + "mix.o": (W, m.heads * m.vdim)})
+            if m.v_mix:
+                s[p + "mix.vmix"] = ()
+        f = L.mlp
+        if f:
+            s[p + "mlp.router"] = (f.experts, W)
+            for e in range(f.experts):
+                s.update({f"{p}mlp.e{e}.gate": (f.ff, W), f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
+            if f.shared_ff:
+                s.update({p + "mlp.shared.gate": (f.shared_ff, W), p + "mlp.shared.up": (f.shared_ff, W),
+                          p + "mlp.shared.down": (W, f.shared_ff)})
+    return s
+
+
+def random_weights(cfg: HybridConfig, seed: int = 0, std: float | None = None) -> dict[str, torch.Tensor]:
+    """Seeded random weights under the checkpoint names (bf16), scaled so that activations stay O(1) through the layers."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf == "alpha":
+            t = 0.5 + 0.5 * torch.rand((), generator=g)
+        elif leaf == "vmix":
+            t = 0.2 + 0.5 * torch.rand((), generator=g)
+        elif leaf == "b" and len(shape) == 1:
+            t = 0.05 * torch.randn(shape, generator=g)
+        elif leaf in ("norm1", "norm2", "norm1b", "norm2b", "norm") and len(shape) == 1:
+            t = 1.0 + 0.1 * torch.randn(shape, generator=g)
+        elif leaf == "A_log":
+            t = torch.log(0.5 + 1.5 * torch.rand(shape, generator=g))
+        elif leaf == "dt_bias":
+            t = -2.0 + 1.5 * torch.rand(shape, generator=g)
+        elif leaf in ("D", "sink"):
+            t = torch.randn(shape, generator=g)
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=g) / shape[1] ** 0.5
+        elif len(shape) == 2:
+            t = torch.randn(shape, generator=g) * (std if std is not None else shape[1] ** -0.5)
+        else:
+            t = 0.1 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ the ragged step
+@dataclass
+class StepMeta:
+    """Index tensors of one step (device int32 unless noted).  Sequence s of the step owns block-table row / state slot
+    seq_slot[s], brings tokens [seq_start[s], seq_start[s+1]) and continues at position seq_pos0[s]."""
+    num_seqs: int
+    num_tokens: int
+    seq_start: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_pos0: torch.Tensor
+    tok_seq: torch.Tensor
+    tok_row: torch.Tensor
+    tok_pos: torch.Tensor
+    slot_mapping: torch.Tensor  # int64 [T]: KV slot = block id * block_size + offset
+
+    @staticmethod
+    def build(entries, block_rows, block_size: int, device) -> "StepMeta":
+        """entries: [(row, pos0, n_new)]; block_rows: row -> list of block ids (host mirror of the block table).
+        One pinned staging tensor, one asynchronous copy."""
+        import numpy as np
+
+        b = len(entries)
+        n = np.array([e[2] for e in entries], dtype=np.int64)
+        t = int(n.sum())
+        start = np.zeros(b + 1, dtype=np.int64)
+        np.cumsum(n, out=start[1:])
+        rows = np.array([e[0] for e in entries], dtype=np.int64)
+        pos0 = np.array([e[1] for e in entries], dtype=np.int64)
+        tok_seq = np.repeat(np.arange(b, dtype=np.int64), n)
+        tok_pos = np.arange(t, dtype=np.int64) - start[tok_seq] + pos0[tok_seq]
+        slots = np.empty(t, dtype=np.int64)
+        for s, (row, p0, k) in enumerate(entries):
+            blocks = np.asarray(block_rows[row], dtype=np.int64)
+            p = np.arange(p0, p0 + k)
+            slots[start[s]:start[s + 1]] = blocks[p // block_size] * block_size + p % block_size
+        parts = [start, rows, pos0, tok_seq, rows[tok_seq], tok_pos]
+        i32 = np.concatenate(parts).astype(np.int32)
+        if i32.size % 2:  # the int64 slots that follow must start on an 8-byte boundary
+            i32 = np.concatenate([i32, np.zeros(1, np.int32)])
+        host = torch.from_numpy(np.concatenate([i32, slots.view(np.int32)]))
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(device, non_blocking=True)
+        cut, o = [], 0
+        for a in parts:
+            cut.append(dev[o:o + a.size])
+            o += a.size
+        return StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64))
+
+
+# ------------------------------------------------------------------------------------------------ the model
+class HybridCausalLM:
+    """Weights, KV pools, recurrent state and the step function of a hybrid decoder.  Rows of `block_table` and slots of the
+    recurrent state are the model runner's persistent per-request rows."""
+
+    mixed_batch = True  # prompt portions and decoded tokens of many requests run as one ragged batch
+
+    def __init__(self, cfg: HybridConfig, weights, *, num_blocks: int, max_num_seqs: int, max_model_len: int,
+                 block_size: int = 32, device="cuda", dtype=torch.bfloat16):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"hybrid decoders run in bfloat16 or float32, not {dtype}")
+        self.cfg, self.device, self.et = cfg, torch.device(device), dtype
+        ops.device_check(self.device.index or 0)
+        self.block_size, self.num_blocks = block_size, num_blocks
+        self.max_num_seqs, self.max_model_len = max_num_seqs, max_model_len
+        self.max_blocks = -(-max_model_len // block_size)
+        self.pad_row = max_num_seqs
+        dev, et = self.device, dtype
+        if weights is None:
+            weights = random_weights(cfg)
+        want = tensor_shapes(cfg)
+
+        def get(name):
+            t = weights[name]
+            if tuple(t.shape) != want[name]:
+                raise ValueError(f"tensor {name!r} has shape {tuple(t.shape)}, the configuration says {want[name]}")
+            return t
+
+        def lin(*names):  # GEMM operand: rows of several tensors stacked
+            return torch.cat([get(n) for n in names], dim=0).to(dev, et).contiguous()
+
+        def vec(name):
+            return get(name).to(dev, torch.float32).contiguous()
+
+        def norm(name):
+            return (vec(name), vec(name + ".b"), float(get(name + ".alpha").float()))
+
+        self.embed, self.head = lin("embed"), lin("head")
+        self.final_norm = norm("final.norm")
+        self.layers = []
+        slots = max_num_seqs + 1
+        first_vmix = True
+        for i, L in enumerate(cfg.layers):
+            p, m = f"l{i}.", L.mixer
+            lw = {"spec": L, "norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b")}
+            if L.kind == "mamba2":
+                lw.update(w_in=lin(p + "mix.in"), conv_w=vec(p + "mix.conv"), conv_b=vec(p + "mix.conv.b"),
+                          dt_bias=vec(p + "mix.dt_bias"), a_log=vec(p + "mix.A_log"), d=vec(p + "mix.D"),
+                          gnorm=vec(p + "mix.norm"), w_o=lin(p + "mix.o"),
+                          conv_state=torch.zeros((slots, m.conv - 1, m.channels), dtype=torch.float32, device=dev),
+                          ssm_state=torch.zeros((slots, m.heads, m.state, m.vdim), dtype=torch.float32, device=dev))
+            else:
+                lw.update(w_qkv=lin(p + "mix.q", p + "mix.k", p + "mix.v"), sink=vec(p + "mix.sink"), w_o=lin(p + "mix.o"),
+                          k_pool=torch.zeros((num_blocks, m.kv_heads, block_size, m.dim), dtype=et, device=dev),
+                          v_pool=torch.zeros((num_blocks, m.kv_heads, block_size, m.vdim), dtype=et, device=dev))
+                lw["vmix_mode"] = 0
+                if m.v_mix:
+                    lw["vmix_mode"] = 1 if first_vmix else 2
+                    lw["lam"] = float(get(p + "mix.vmix").float())
+                    if first_vmix:
+                        self._vfirst_cols = m.kv_heads * m.vdim
+                    elif m.kv_heads * m.vdim != self._vfirst_cols:
+                        raise ValueError("value mixing needs the same kv_heads * vdim in every v_mix layer")
+                    first_vmix = False
+            f = L.mlp
+            if f:
+                lw.update(norm2=norm(p + "norm2"), norm2b=norm(p + "norm2b"), w_router=lin(p + "mlp.router"))
+                lw["w_gu"] = torch.stack([torch.cat([get(f"{p}mlp.e{e}.gate"), get(f"{p}mlp.e{e}.up")]) for e in range(f.experts)]
+                                         ).to(dev, et).contiguous()
+                lw["w_down"] = torch.stack([get(f"{p}mlp.e{e}.down") for e in range(f.experts)]).to(dev, et).contiguous()
+                if f.shared_ff:
+                    lw["sh_gu"] = lin(p + "mlp.shared.gate", p + "mlp.shared.up")
+                    lw["sh_down"] = lin(p + "mlp.shared.down")
+            self.layers.append(lw)
+        self.block_table = torch.zeros((slots, self.max_blocks), dtype=torch.int32, device=dev)
+        self.num_tokens = torch.zeros((slots,), dtype=torch.int32, device=dev)
+        self.gemm_ws = None
+        self.last_logits = None
+        self.last_logprobs = None
+
+    # ------------------------------------------------------------------ sizes
+    def kv_bytes_per_block(self) -> int:
+        es = 2 if self.et == torch.bfloat16 else 4
+        return sum(L.mixer.kv_heads * self.block_size * (L.mixer.dim + L.mixer.vdim) * es
+                   for L in self.cfg.layers if L.kind == "attention")
+
+    def state_bytes_per_slot(self) -> int:
+        return sum(4 * (L.mixer.heads * L.mixer.state * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
+                   for L in self.cfg.layers if L.kind == "mamba2")
+
+    # ------------------------------------------------------------------ building blocks
+    def _linear(self, a, w):
+        """fp32 [M, N] = a @ w^T.  bf16 serving: the tcgen05 GEMM (TMA needs K * 2 bytes to be a multiple of 16); anything
+        else, and all of 32-bit serving, runs on the CUDA cores with true fp32 arithmetic."""
+        if self.et == torch.bfloat16 and w.shape[1] % 8 == 0:
+            m, (n, k) = a.shape[0], w.shape
+            need = ops.gemm_workspace_bytes(m, n, k, ops.BF16, 0)
+            if need and (self.gemm_ws is None or self.gemm_ws.numel() < need):
+                self.gemm_ws = torch.zeros(need, dtype=torch.uint8, device=self.device)  # stream-K counters start at zero
+            return ops.gemm(a, w, out_dtype=torch.float32, workspace=self.gemm_ws if need else None)
+        return ops.linear_simt(a, w)
+
+    def _ssm(self, lw, h, meta):
+        m = lw["spec"].mixer
+        proj = self._linear(h, lw["w_in"])  # fp32 [T, z | x | B | C | dt]
+        xbc = ops.causal_conv_silu(proj, m.inner, m.channels, lw["conv_w"], lw["conv_b"], lw["conv_state"], meta, self.et)
+        y = ops.ssd_scan(xbc, proj, m.inner + m.channels, lw["a_log"], lw["dt_bias"], lw["d"], lw["ssm_state"], meta, m.heads,
+                         m.vdim, m.state, m.groups)
+        g = ops.gated_group_rmsnorm(y, proj, lw["gnorm"], m.norm_groups, self.cfg.eps, self.et)
+        return self._linear(g, lw["w_o"])
+
+    def _attention(self, lw, h, meta, ctx):
+        m = lw["spec"].mixer
+        qkv = self._linear(h, lw["w_qkv"])  # fp32 [T, q | k | v]
+        kc, vc = m.heads * m.dim, (m.heads + m.kv_heads) * m.dim
+        mode = lw["vmix_mode"]
+        if mode == 1:
+            ctx["v_first"] = torch.empty((h.shape[0], self._vfirst_cols), dtype=torch.float32, device=self.device)
+        ops.kv_write_vmix(qkv, kc, vc, lw["k_pool"], lw["v_pool"], meta.slot_mapping, v_first=ctx.get("v_first"),
+                          lam=lw.get("lam", 0.0), mode=mode)
+        a = ops.swa_sink_attn(qkv, m.heads, lw["k_pool"], lw["v_pool"], self.block_table, meta, lw["sink"], m.scale,
+                              min(m.window, _NO_WINDOW))
+        return self._linear(a, lw["w_o"])
+
+    def _moe(self, lw, h):
+        f = lw["spec"].mlp
+        idx, wt = ops.moe_router(h, lw["w_router"], f.top)
+        pairs = ops.moe_experts(h, wt, ops.moe_align(idx, f.experts), lw["w_gu"], lw["w_down"], f.top, f.limit)
+        shared = None
+        if f.shared_ff:
+            shared = self._linear(ops.clamped_glu(self._linear(h, lw["sh_gu"]), f.shared_limit, self.et), lw["sh_down"])
+        return pairs, shared
+
+    # ------------------------------------------------------------------ the step
+    def forward(self, tokens: torch.Tensor, meta: StepMeta, logit_rows: torch.Tensor | None, capture: list | None = None):
+        """tokens int32 [T] (device) of the ragged batch `meta`; returns fp32 logits [len(logit_rows), vocab] (None when no
+        row is asked for).  KV pools and recurrent state of the sequences advance by the step's tokens.
+        capture: a list that is given, layer by layer, a copy of x as that layer leaves it."""
+        et, n = self.et, len(self.layers)
+        x = ops.embed_scale(tokens, self.embed, self.cfg.embed_scale)
+        h = ops.dyt_norm(x, *self.layers[0]["norm1"], et) if n else None
+        ctx: dict = {}
+        for i, lw in enumerate(self.layers):
+            nxt = self.layers[i + 1]["norm1"] if i + 1 < n else self.final_norm
+            y = self._ssm(lw, h, meta) if lw["spec"].kind == "mamba2" else self._attention(lw, h, meta, ctx)
+            if lw["spec"].mlp:
+                h2 = ops.dyt_residual(x, y, lw["norm1b"], lw["norm2"], et)
+                pairs, shared = self._moe(lw, h2)
+                h = ops.dyt_residual(x, pairs, lw["norm2b"], nxt, et, y2=shared, nsum=lw["spec"].mlp.top)
+            else:
+                h = ops.dyt_residual(x, y, lw["norm1b"], nxt, et)
+            if capture is not None:
+                capture.append(x.clone())
+        if not n:
+            h = ops.dyt_norm(x, *self.final_norm, et)
+        if logit_rows is None or logit_rows.numel() == 0:
+            self.last_logits = None
+            return None
+        self.last_logits = self._linear(h.index_select(0, logit_rows).contiguous(), self.head)
+        return self.last_logits

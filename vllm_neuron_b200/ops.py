@@ -589,3 +589,215 @@ def allreduce_rmsnorm(peer_bufs, peer_flags, epoch, rank, world, t, h, norm_w, e
         check(fn(first, peer_flags, _ptr(epoch), rank, world, _ptr(x), _ptr(norm_w), _ptr(y), _ptr(q), _ptr(s), t, h,
                  float(eps), qd, _stream()), name)
     return x, q, s
+
+
+# ------------------------------------------------------------------ hybrid decoders (state-space + windowed attention + MoE)
+# The residual stream and every norm / recurrence tensor is fp32; tensors that feed a GEMM or live in a KV pool are bf16
+# (bf16 serving) or fp32 (32-bit serving).  `meta` is a StepMeta-like object with the ragged-batch index tensors.
+def _edt(t):
+    if t is torch.bfloat16 or (hasattr(t, "dtype") and t.dtype == torch.bfloat16):
+        return BF16
+    if t is torch.float32 or (hasattr(t, "dtype") and t.dtype == torch.float32):
+        return F32
+    raise _cabi.B200Error(f"element type {t} is neither bfloat16 nor float32")
+
+
+def _f32(*ts):
+    for t in ts:
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise _cabi.B200Error("expected a contiguous fp32 tensor")
+
+
+def embed_scale(tokens, table, scale: float):
+    """tokens int32 [T] -> fp32 [T, W] = table[token] * scale."""
+    _cuda(tokens, table)
+    assert tokens.dtype == torch.int32 and table.is_contiguous()
+    t, (v, w) = tokens.numel(), table.shape
+    out = torch.empty((t, w), dtype=torch.float32, device=table.device)
+    with _k("embed_scale"):
+        check(_cabi.load().b200_embed_scale(_ptr(tokens), _ptr(table), _edt(table), _ptr(out), t, w, v, float(scale), _stream()),
+              "b200_embed_scale")
+    return out
+
+
+def dyt_norm(x, w, b, alpha: float, out_dtype):
+    _cuda(x, w, b)
+    _f32(x, w, b)
+    t, width = x.shape
+    out = torch.empty((t, width), dtype=out_dtype, device=x.device)
+    with _k("dyt_norm"):
+        check(_cabi.load().b200_dyt_norm(_ptr(x), _ptr(w), _ptr(b), float(alpha), _ptr(out), _edt(out), t, width, _stream()),
+              "b200_dyt_norm")
+    return out
+
+
+def dyt_residual(x, y, norm, next_norm=None, out_dtype=torch.bfloat16, y2=None, nsum: int = 1):
+    """x += dyt(sum of the nsum consecutive rows of y per token [+ y2]); returns dyt_next(x) in out_dtype (or None).
+    norm / next_norm: (w, b, alpha)."""
+    _cuda(x, y, y2)
+    _f32(x, y, y2)
+    t, width = x.shape
+    assert y.shape == (t * nsum, width) and (y2 is None or y2.shape == (t, width))
+    out2 = torch.empty((t, width), dtype=out_dtype, device=x.device) if next_norm is not None else None
+    w2, b2, a2 = next_norm if next_norm is not None else (None, None, 0.0)
+    with _k("dyt_residual"):
+        check(_cabi.load().b200_dyt_residual(_ptr(x), _ptr(y), nsum, _ptr(y2), _ptr(norm[0]), _ptr(norm[1]), float(norm[2]),
+                                             _ptr(w2), _ptr(b2), float(a2), _ptr(out2), _edt(out_dtype), t, width, _stream()),
+              "b200_dyt_residual")
+    return out2
+
+
+def gated_group_rmsnorm(y, z_src, w, groups: int, eps: float, out_dtype):
+    """y fp32 [T, inner]; z = the first `inner` columns of the fp32 rows z_src (any pitch)."""
+    _cuda(y, z_src, w)
+    _f32(y, w)
+    assert z_src.dtype == torch.float32 and z_src.stride(1) == 1
+    t, inner = y.shape
+    out = torch.empty((t, inner), dtype=out_dtype, device=y.device)
+    with _k("gated_group_rmsnorm"):
+        check(_cabi.load().b200_gated_group_rmsnorm(_ptr(y), _ptr(z_src), z_src.stride(0), _ptr(w), _ptr(out), _edt(out), t, inner,
+                                                    groups, float(eps), _stream()), "b200_gated_group_rmsnorm")
+    return out
+
+
+def clamped_glu(gate_up, limit: float, out_dtype):
+    _cuda(gate_up)
+    _f32(gate_up)
+    t, ff2 = gate_up.shape
+    out = torch.empty((t, ff2 // 2), dtype=out_dtype, device=gate_up.device)
+    with _k("clamped_glu"):
+        check(_cabi.load().b200_clamped_glu(_ptr(gate_up), _ptr(out), _edt(out), t, ff2 // 2, float(limit), _stream()),
+              "b200_clamped_glu")
+    return out
+
+
+def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta, out_dtype):
+    """Columns [col0, col0 + channels) of the fp32 rows `src` -> SiLU(conv) [T, channels]; `state` [slots, taps-1, channels]
+    fp32 is read for continuing sequences and updated for all."""
+    _cuda(src, conv_w, conv_b, state)
+    _f32(src, conv_w, conv_b, state)
+    t, taps = src.shape[0], conv_w.shape[1]
+    assert conv_w.shape[0] == channels and state.shape[1:] == (taps - 1, channels)
+    out = torch.empty((t, channels), dtype=out_dtype, device=src.device)
+    with _k("causal_conv_silu"):
+        check(_cabi.load().b200_causal_conv_silu(_ptr(src), src.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(state),
+                                                 _ptr(meta.tok_seq), _ptr(meta.seq_start), _ptr(meta.seq_slot), _ptr(meta.seq_pos0),
+                                                 _ptr(out), _edt(out), t, meta.num_seqs, channels, taps, _stream()),
+              "b200_causal_conv_silu")
+    return out
+
+
+def ssd_scan(xbc, dt_src, dt_col0: int, a_log, dt_bias, d_skip, state, meta, heads: int, vdim: int, nstate: int, groups: int):
+    """xbc [T, H*P + 2*G*N] (bf16 | fp32), raw dt = columns [dt_col0, dt_col0 + H) of the fp32 rows dt_src; state fp32
+    [slots, H, N, P] updated in place; returns y fp32 [T, H*P]."""
+    _cuda(xbc, dt_src, state)
+    _f32(dt_src, a_log, dt_bias, d_skip, state)
+    assert xbc.is_contiguous() and state.shape[1:] == (heads, nstate, vdim)
+    t = xbc.shape[0]
+    y = torch.empty((t, heads * vdim), dtype=torch.float32, device=xbc.device)
+    with _k("ssd_scan"):
+        check(_cabi.load().b200_ssd_scan(_ptr(xbc), _edt(xbc), xbc.shape[1], _ptr(dt_src), dt_src.stride(0), dt_col0, _ptr(a_log),
+                                         _ptr(dt_bias), _ptr(d_skip), _ptr(state), _ptr(meta.seq_start), _ptr(meta.seq_slot),
+                                         _ptr(meta.seq_pos0), _ptr(y), meta.num_seqs, heads, vdim, nstate, groups, _stream()),
+              "b200_ssd_scan")
+    return y
+
+
+def kv_write_vmix(qkv, k_col0: int, v_col0: int, k_pool, v_pool, slot_mapping, *, v_first=None, lam: float = 0.0, mode: int = 0):
+    """Pools [num_blocks, G, block_size, D] / [.., Dv].  mode 0 plain, 1 record v_first, 2 mix with v_first before caching."""
+    _cuda(qkv, k_pool, v_pool, slot_mapping, v_first)
+    _f32(qkv, v_first)
+    assert slot_mapping.dtype == torch.int64 and k_pool.dtype == v_pool.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+    _, g, bs, d = k_pool.shape
+    dv = v_pool.shape[3]
+    with _k("kv_write_vmix"):
+        check(_cabi.load().b200_kv_write_vmix(_ptr(qkv), qkv.stride(0), k_col0, v_col0, _ptr(v_first), float(lam), mode,
+                                              _ptr(k_pool), _ptr(v_pool), _edt(k_pool), _ptr(slot_mapping), qkv.shape[0], g, d, dv,
+                                              bs, _stream()), "b200_kv_write_vmix")
+
+
+def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int):
+    """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type."""
+    _cuda(q_src, k_pool, v_pool, block_table, sink)
+    _f32(q_src, sink)
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    _, g, bs, d = k_pool.shape
+    dv = v_pool.shape[3]
+    t = q_src.shape[0]
+    out = torch.empty((t, num_heads * dv), dtype=k_pool.dtype, device=q_src.device)
+    with _k("swa_sink_attn"):
+        check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
+                                              _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
+                                              _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, bs,
+                                              _stream()), "b200_swa_sink_attn")
+    return out
+
+
+def moe_router(h, w_router, top: int):
+    """-> (expert ids int32 [T, top], routing weights fp32 [T, top] = sigmoid scores of the chosen experts)."""
+    _cuda(h, w_router)
+    assert h.dtype == w_router.dtype and h.is_contiguous() and w_router.is_contiguous()
+    t, width = h.shape
+    e = w_router.shape[0]
+    idx = torch.empty((t, top), dtype=torch.int32, device=h.device)
+    wt = torch.empty((t, top), dtype=torch.float32, device=h.device)
+    with _k("moe_router"):
+        check(_cabi.load().b200_moe_router(_ptr(h), _ptr(w_router), _edt(h), _ptr(idx), _ptr(wt), t, width, e, top, _stream()),
+              "b200_moe_router")
+    return idx, wt
+
+
+def moe_tile_rows() -> int:
+    return int(_cabi.load().b200_moe_tile_rows())
+
+
+def moe_align(topk_idx, num_experts: int):
+    """-> (sorted pair ids int32 [cap] padded with -1, tile owners int32 [max_tiles], device count of used tiles [1])."""
+    _cuda(topk_idx)
+    assert topk_idx.dtype == torch.int32 and topk_idx.is_contiguous()
+    n, bm = topk_idx.numel(), moe_tile_rows()
+    max_tiles = -(-n // bm) + num_experts
+    dev = topk_idx.device
+    sorted_ids = torch.empty(max_tiles * bm, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    with _k("moe_align"):
+        check(_cabi.load().b200_moe_align(_ptr(topk_idx), n, num_experts, _ptr(sorted_ids), sorted_ids.numel(), _ptr(tile_expert),
+                                          max_tiles, _ptr(num_tiles), _stream()), "b200_moe_align")
+    return sorted_ids, tile_expert, num_tiles
+
+
+def linear_simt(a, w):
+    """fp32 [M, N] = a [M, K] @ w [N, K]^T with fp32 accumulation on the CUDA cores: fp32 operands, or shapes the tensor-core
+    GEMM does not take."""
+    _cuda(a, w)
+    assert a.dtype == w.dtype and a.stride(1) == 1 and w.is_contiguous() and a.shape[1] == w.shape[1]
+    m, k = a.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    with _k(f"linear_simt[{m}x{n}x{k}]"):
+        check(_cabi.load().b200_grouped_linear(_ptr(a), a.stride(0), 0, 0, 0, _ptr(w), 0, 0, 0, -(-m // moe_tile_rows()), m, n, k,
+                                               _edt(a), _ptr(out), n, 0, 0, 0.0, _stream()), "b200_grouped_linear")
+    return out
+
+
+def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float):
+    """Routed experts: for every (token, choice) pair  W_down glu(W_gate_up (weight * h)).  h [T, W]; w_gate_up
+    [E, 2 ff, W] (gate rows first), w_down [E, W, ff]; returns fp32 [T * top, W] in pair order."""
+    _cuda(h, topk_weight, w_gate_up, w_down)
+    sorted_ids, tile_expert, num_tiles = align
+    e, ff2, width = w_gate_up.shape
+    ff = ff2 // 2
+    tiles = tile_expert.numel()
+    act = torch.empty((sorted_ids.numel(), ff), dtype=h.dtype, device=h.device)
+    out = torch.empty((h.shape[0] * top, width), dtype=torch.float32, device=h.device)
+    lib = _cabi.load()
+    with _k("moe_gate_up_glu"):
+        check(lib.b200_grouped_linear(_ptr(h), h.stride(0), _ptr(sorted_ids), top, _ptr(topk_weight), _ptr(w_gate_up), ff2 * width,
+                                      _ptr(tile_expert), _ptr(num_tiles), tiles, 0, ff, width, _edt(h), _ptr(act), ff, 0, 1,
+                                      float(limit), _stream()), "b200_grouped_linear")
+    with _k("moe_down"):
+        check(lib.b200_grouped_linear(_ptr(act), ff, _ptr(sorted_ids), 0, 0, _ptr(w_down), width * ff, _ptr(tile_expert),
+                                      _ptr(num_tiles), tiles, 0, width, ff, _edt(h), _ptr(out), width, 1, 0, 0.0, _stream()),
+              "b200_grouped_linear")
+    return out

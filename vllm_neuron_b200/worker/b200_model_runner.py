@@ -91,6 +91,11 @@ class B200ModelRunner:
         self.num_blocks: int | None = None
         self.use_cuda_graph = not getattr(self.model_config, "enforce_eager", False)
         self._stage = None
+        # models whose step is one ragged batch (model.mixed_batch): positions of this step's portion whose fp32 logits the
+        # caller wants back (req_id -> [index in the portion]); the rows come back in tap_logits (req_id -> device [n, vocab])
+        self.logit_taps: dict[str, list[int]] = {}
+        self.tap_logits: dict[str, torch.Tensor] = {}
+        self.output_factory = None  # (empty_output, output_class); None = vLLM's ModelRunnerOutput
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         import numpy as np
@@ -412,16 +417,116 @@ class B200ModelRunner:
             ids.append(i); lps.append(l); rks.append(r)
         return LogprobsLists(np.concatenate(ids), np.concatenate(lps), np.concatenate(rks))
 
+    # ------------------------------------------------------------------ ragged-batch models (model.mixed_batch)
+    def _output_types(self):
+        if self.output_factory is not None:
+            return self.output_factory
+        from vllm.v1.outputs import EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput
+
+        return EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput
+
+    def extend_prompt(self, req_id: str, tokens) -> None:
+        """Teacher forcing: append known tokens to a live request; the next steps compute them like prompt tokens (no
+        sampling until all known tokens are computed)."""
+        st = self.requests[req_id]
+        assert not st.output_token_ids, "a request that has generated tokens cannot take forced ones"
+        st.prompt_token_ids.extend(int(t) for t in tokens)
+
+    def _execute_mixed(self, so, output_cls):
+        """One step of a model whose forward is a single ragged batch: every scheduled request brings its next n tokens
+        (a prompt portion, or the last sampled token), all run together, and the requests whose known tokens are now all
+        computed sample their next token.  State slot and block-table row of a request are its persistent row."""
+        from ..hybrid import StepMeta
+
+        entries, toks, sample_rows, sample_sts, tap_rows, tap_ids, no_sample = [], [], [], [], [], [], []
+        order = [nr.req_id for nr in so.scheduled_new_reqs] + [r for r in so.scheduled_cached_reqs.req_ids
+                                                               if r in so.num_scheduled_tokens]
+        off = 0
+        for rid in order:
+            st = self.requests[rid]
+            n = so.num_scheduled_tokens[rid]
+            start = st.num_computed_tokens
+            np_, no_ = len(st.prompt_token_ids), len(st.output_token_ids)
+            assert n > 0 and start + n <= np_ + no_ <= self.max_model_len, (rid, start, n, np_, no_)
+            assert start > 0 or st.prefilled == 0, "recurrent state cannot start from a cached prefix"
+            seg = st.prompt_token_ids[start:start + n] if start + n <= np_ else \
+                (st.prompt_token_ids[start:] + st.output_token_ids)[:n] if start < np_ else \
+                st.output_token_ids[start - np_:start - np_ + n]
+            toks += seg
+            entries.append((st.row, start, n))
+            for p in self.logit_taps.get(rid, ()):
+                assert 0 <= p < n
+                tap_rows.append(off + p)
+                tap_ids.append(rid)
+            if start + n == np_ + no_:
+                sample_rows.append(off + n - 1)
+                sample_sts.append(st)
+            else:
+                no_sample.append(rid)
+            st.num_computed_tokens = start + n
+            st.prefilled = min(np_, start + n)
+            off += n
+        self.logit_taps = {}
+        dev = self.device
+        meta = StepMeta.build(entries, {st.row: st.block_ids for st in (self.requests[r] for r in order)}, self.block_size, dev)
+        ht = torch.tensor(toks, dtype=torch.int32)
+        hr = torch.tensor(sample_rows + tap_rows, dtype=torch.int64)
+        if dev.type == "cuda":
+            ht, hr = ht.pin_memory(), hr.pin_memory()
+        self.h2d_bytes_last += ht.numel() * 4 + hr.numel() * 8 + (3 * len(entries) + 1 + 3 * off) * 4 + off * 8
+        logits = self.model.forward(ht.to(dev, non_blocking=True), meta, hr.to(dev, non_blocking=True) if hr.numel() else None)
+        ns = len(sample_rows)
+        self.tap_logits = {}
+        for i, rid in enumerate(tap_ids):
+            self.tap_logits.setdefault(rid, []).append(ns + i)
+        self.tap_logits = {rid: logits[rows] for rid, rows in self.tap_logits.items()}
+        sampled: list[list[int]] = []
+        logprobs = None
+        if ns:
+            samp = self._sampling_inputs(sample_sts)
+            nlp = self._num_logprobs(sample_sts)
+            lg = logits[:ns]
+            cv = ci = None
+            if samp is not None or nlp is not None:
+                cv, ci = ops.topk_candidates(lg)
+            if samp is not None:
+                sp_d = torch.tensor(samp[0], dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+                u_d = torch.tensor(samp[1], dtype=torch.float32).pin_memory().to(dev, non_blocking=True)
+                self.h2d_bytes_last += ns * 16
+                ids = ops.sample_candidates(cv, ci, sp_d, u_d)
+            else:
+                ids = ops.argmax(lg)
+            lp_parts = [(ns, None)]
+            if nlp is not None:
+                m, se = ops.row_lse(lg)
+                lp_parts = [(ns, ops.gather_logprobs(cv, ci, ids, m, se, nlp))]
+            self._pin_out[:ns].copy_(ids, non_blocking=True)
+            lp_host = self._logprobs_to_host(lp_parts)
+            torch.cuda.current_stream().synchronize()
+            self.d2h_bytes_last += ns * 8
+            sampled = [[x] for x in self._np_out[:ns].tolist()]
+            logprobs = self._logprobs_lists(lp_host)
+        else:
+            torch.cuda.current_stream().synchronize()
+        req_ids = [st.req_id for st in sample_sts]
+        for st, row in zip(sample_sts, sampled):
+            st.output_token_ids.extend(row)
+        req_ids += no_sample
+        sampled += [[] for _ in no_sample]
+        return output_cls(req_ids=req_ids, req_id_to_index={r: i for i, r in enumerate(req_ids)}, sampled_token_ids=sampled,
+                          logprobs=logprobs, prompt_logprobs_dict={}, pooler_output=[])
+
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
     def execute_model(self, scheduler_output, intermediate_tensors=None):
-        from vllm.v1.outputs import EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput
-
+        EMPTY_MODEL_RUNNER_OUTPUT, ModelRunnerOutput = self._output_types()
         self.h2d_bytes_last = self.d2h_bytes_last = 0
         updates = self._update_states(scheduler_output)
         if not scheduler_output.total_num_scheduled_tokens:
             return EMPTY_MODEL_RUNNER_OUTPUT  # RUNNER:272-274
         self._push_block_updates(updates)
+        if getattr(self.model, "mixed_batch", False):
+            return self._execute_mixed(scheduler_output, ModelRunnerOutput)
 
         req_ids: list[str] = []
         pending: list[torch.Tensor] = []
