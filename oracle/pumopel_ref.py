@@ -36,6 +36,19 @@ def causal_conv_silu(u, w, b):
     return F.silu(out)
 
 
+def selective_scan(x, B, C, dt_raw, dt_bias, A_log, D, S0=None):
+    """x [T, H, P]; B, C [T, H, N] (already expanded per head); dt_raw [T, H].  Returns y [T, H, P]."""
+    T, H, P = x.shape
+    dt = F.softplus(dt_raw + dt_bias)                       # no clamp
+    decay = torch.exp(-torch.exp(A_log) * dt)
+    S = x.new_zeros(H, B.shape[-1], P) if S0 is None else S0.clone()
+    y = x.new_zeros(T, H, P)
+    for t in range(T):
+        S = decay[t, :, None, None] * S + dt[t, :, None, None] * B[t, :, :, None] * x[t, :, None, :]
+        y[t] = torch.einsum("hnp,hn->hp", S, C[t]) + D[:, None] * x[t]
+    return y
+
+
 def mamba2_mixer(h, W, p, m, eps):
     """h [T, width].  m: heads, vdim, state, groups, conv, norm_groups."""
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
@@ -48,17 +61,28 @@ def mamba2_mixer(h, W, p, m, eps):
     x = x.view(T, H, P)
     B = B.view(T, G, N).repeat_interleave(H // G, dim=1)   # head h reads group h // (H / G)
     C = C.view(T, G, N).repeat_interleave(H // G, dim=1)
-    dt = F.softplus(dt + W[p + "dt_bias"])                  # [T, H], no clamp
-    decay = torch.exp(-torch.exp(W[p + "A_log"]) * dt)      # [T, H]
-    S = h.new_zeros(H, N, P)
-    y = h.new_zeros(T, H, P)
-    for t in range(T):
-        S = decay[t, :, None, None] * S + dt[t, :, None, None] * B[t, :, :, None] * x[t, :, None, :]
-        y[t] = torch.einsum("hnp,hn->hp", S, C[t]) + W[p + "D"][:, None] * x[t]
+    y = selective_scan(x, B, C, dt, W[p + "dt_bias"], W[p + "A_log"], W[p + "D"])
     y = y.reshape(T, inner) * F.silu(z)                     # gate first, normalise second
     ng = m["norm_groups"]
     y = rms_unit(y.view(T, ng, inner // ng), eps).reshape(T, inner) * W[p + "norm"]
     return y @ W[p + "o"].T
+
+
+def sink_window_attention(q, k, v, sink, scale, window):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] of one sequence -> [T, H * Dv].  query i attends keys i - window < j <= i;
+    the softmax runs over those scores and one extra per-head logit `sink` that is dropped afterwards."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    kk = k.repeat_interleave(H // G, dim=1)
+    vv = v.repeat_interleave(H // G, dim=1)
+    s = torch.einsum("ihd,jhd->hij", q, kk) * scale
+    i = torch.arange(T)[:, None]
+    j = torch.arange(T)[None, :]
+    seen = (i - j >= 0) & (i - j < window)
+    s = s.masked_fill(~seen, -math.inf)
+    sk = sink.to(s.dtype)[:, None, None].expand(H, T, 1)
+    pr = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :T]
+    return torch.einsum("hij,jhd->ihd", pr, vv).reshape(T, H * v.shape[-1])
 
 
 def swa_sink_attention(h, W, p, m, v_first):
@@ -72,16 +96,7 @@ def swa_sink_attention(h, W, p, m, v_first):
     if m.get("v_mix") and v_first is not None:
         lam = W[p + "vmix"]
         v = (1 - lam) * v + lam * v_first
-    kk = k.repeat_interleave(H // G, dim=1)
-    vv = v.repeat_interleave(H // G, dim=1)
-    s = torch.einsum("ihd,jhd->hij", q, kk) * m["scale"]
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
-    seen = (i - j >= 0) & (i - j < m["mask"]["size"])
-    s = s.masked_fill(~seen, -math.inf)
-    sink = W[p + "sink"].to(s.dtype)[:, None, None].expand(H, T, 1)
-    pr = torch.softmax(torch.cat([s, sink], dim=-1), dim=-1)[..., :T]   # the sink has no value
-    o = torch.einsum("hij,jhd->ihd", pr, vv).reshape(T, H * Dv)
+    o = sink_window_attention(q, k, v, W[p + "sink"], m["scale"], m["mask"]["size"] if m.get("mask") else T + 1)
     return o @ W[p + "o"].T, v
 
 

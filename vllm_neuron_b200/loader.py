@@ -143,6 +143,32 @@ class HFCheckpointWeights:
         self._cache.pop(li, None)
 
 
+class CheckpointTensors:
+    """A safetensors checkpoint directory as a read-only name -> tensor mapping under the checkpoint's own tensor names
+    (models whose loader needs no renaming or fusing: the model object stacks what it wants fused)."""
+
+    def __init__(self, path: str):
+        self.path = path
+        self.index = _index_safetensors(path)
+        self._handles: dict = {}
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.index
+
+    def keys(self):
+        return self.index.keys()
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        from safetensors import safe_open
+
+        fn = self.index.get(name)
+        if fn is None:
+            raise CheckpointError(f"tensor {name!r} is missing from the checkpoint at {self.path!r}")
+        if fn not in self._handles:
+            self._handles[fn] = safe_open(fn, framework="pt")
+        return self._handles[fn].get_tensor(name)
+
+
 class _Layers:
     def __init__(self, parent):
         self.parent = parent
