@@ -193,6 +193,153 @@ __global__ void __launch_bounds__(GL_THREADS)
   }
 }
 
+// ---------------------------------------------------------------- bf16 operands: the same contract on the tensor cores
+// mma.sync m16n8k16 (bf16 x bf16 -> fp32).  CTA = 4 warps, 32 rows x (128 outputs | 64 gate + 64 up outputs), K in steps of
+// 32 through shared memory (rows padded to 80 bytes: conflict-free ldmatrix), next tile's global loads in flight during the
+// current tile's MMAs.  The routing weight scales the gathered input row in fp32 before it is rounded to the bf16 operand.
+// Needs K % 8 == 0 and 16-byte aligned rows (the dispatcher checks; otherwise the CUDA-core kernel above runs).
+constexpr int GM_BK = 32;
+constexpr int GM_LD = GM_BK + 8;
+constexpr int GM_WROWS = 128;
+
+template <int EPI>
+__global__ void __launch_bounds__(128)
+    grouped_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
+                       const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ w, int64_t w_stride,
+                       const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles, int M, int N, int K,
+                       void* __restrict__ out, int ldo, int scatter, float limit) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ __align__(16) __nv_bfloat16 As[MOE_BM][GM_LD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[GM_WROWS][GM_LD];
+  __shared__ int32_t rid[MOE_BM];
+  __shared__ int32_t oid[MOE_BM];
+  __shared__ float rsc[MOE_BM];
+  const int tile = blockIdx.x;
+  if (num_tiles && tile >= *num_tiles) return;
+  const int e = tile_expert ? tile_expert[tile] : 0;
+  const __nv_bfloat16* we = w + (int64_t)e * w_stride;
+  constexpr int BN = EPI == GL_EPI_GLU ? 64 : 128;  // outputs per CTA
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MOE_BM) {
+    const int r = tile * MOE_BM + tid;
+    int src = -1, dst = -1;
+    float sc = 1.0f;
+    if (sorted_ids) {
+      const int id = sorted_ids[r];
+      if (id >= 0) {
+        src = gather_div > 0 ? id / gather_div : r;
+        dst = scatter ? id : r;
+        if (row_scale) sc = row_scale[id];
+      }
+    } else if (r < M) {
+      src = dst = r;
+    }
+    rid[tid] = src;
+    oid[tid] = dst;
+    rsc[tid] = sc;
+  }
+  __syncthreads();
+  // global -> register staging: one 16-byte vector of A and four of W per thread and K step
+  const int a_row = tid >> 2, kc = (tid & 3) * 8;
+  const int a_src = rid[a_row];
+  const float a_sc = rsc[a_row];
+  const __nv_bfloat16* w_ptr[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (tid + 128 * i) >> 2;  // 0..127
+    int n, grow;
+    if (EPI == GL_EPI_GLU) {
+      n = n0 + (r & 63);
+      grow = (r < 64 ? 0 : N) + n;
+    } else {
+      n = n0 + r;
+      grow = n;
+    }
+    w_ptr[i] = n < N ? we + (int64_t)grow * K : nullptr;
+  }
+  uint4 ra, rw[4];
+  auto fetch = [&](int k0) {
+    const bool kin = k0 + kc < K;
+    ra = make_uint4(0, 0, 0, 0);
+    if (a_src >= 0 && kin) {
+      ra = *reinterpret_cast<const uint4*>(a + (int64_t)a_src * lda + k0 + kc);
+      if (a_sc != 1.0f) {
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ra);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          h2[i] = __floats2bfloat162_rn(f.x * a_sc, f.y * a_sc);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      rw[i] = (w_ptr[i] && kin) ? *reinterpret_cast<const uint4*>(w_ptr[i] + k0 + kc) : make_uint4(0, 0, 0, 0);
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  // first shared-memory row of this warp's n8 tile j
+  auto nrow = [&](int j) { return EPI == GL_EPI_GLU ? (j < 2 ? 16 * warp + 8 * j : 64 + 16 * warp + 8 * (j - 2)) : 32 * warp + 8 * j; };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += GM_BK) {
+    *reinterpret_cast<uint4*>(&As[a_row][kc]) = ra;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(&Ws[(tid + 128 * i) >> 2][kc]) = rw[i];
+    __syncthreads();
+    if (k0 + GM_BK < K) fetch(k0 + GM_BK);
+#pragma unroll
+    for (int kk = 0; kk < GM_BK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) ldmatrix_x4(af[mt], smem_u32(&As[mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        uint32_t bf[4];
+        const int mi = lane >> 3;  // matrix of the x4 load: tile 2 jp + mi / 2, k half mi % 2
+        ldmatrix_x4(bf, smem_u32(&Ws[nrow(2 * jp + (mi >> 1)) + (lane & 7)][kk + (mi & 1) * 8]));
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16_16816(acc[mt][2 * jp], af[mt], bf[0], bf[1]);
+          mma_bf16_16816(acc[mt][2 * jp + 1], af[mt], bf[2], bf[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = mt * 16 + (lane >> 2) + (c >= 2 ? 8 : 0);
+      const int dst = oid[r];
+      if (dst < 0) continue;
+      const int col = 2 * (lane & 3) + (c & 1);
+      if (EPI == GL_EPI_GLU) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + 16 * warp + 8 * j + col;
+          if (n >= N) continue;
+          const float g = fminf(acc[mt][j][c], limit);
+          const float u = fminf(fmaxf(acc[mt][j + 2][c], -limit), limit);
+          ((__nv_bfloat16*)out)[(int64_t)dst * ldo + n] = __float2bfloat16_rn(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + 32 * warp + 8 * j + col;
+          if (n < N) ((float*)out)[(int64_t)dst * ldo + n] = acc[mt][j][c];
+        }
+      }
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -236,8 +383,20 @@ int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int g
   B200_REQUIRE(N > 0 && K > 0 && row_tiles >= 0, "grouped_linear: bad shape N=%d K=%d", N, K);
   B200_REQUIRE(sorted_ids || (!tile_expert && !num_tiles && !row_scale), "grouped_linear: expert tiles need the sorted pair list");
   if (row_tiles == 0) return B200_OK;
-  dim3 grid(row_tiles, (N + GL_BN - 1) / GL_BN);
   cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == B200_BF16 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
+    using BT = __nv_bfloat16;
+    if (glu)
+      B200_CUDA_OK(launch_kernel(grouped_mma_kernel<GL_EPI_GLU>, dim3(row_tiles, (N + 63) / 64), dim3(128), 0, st, (const BT*)a, lda,
+                                 sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N, K,
+                                 out, ldo, scatter, limit));
+    else
+      B200_CUDA_OK(launch_kernel(grouped_mma_kernel<GL_EPI_STORE>, dim3(row_tiles, (N + 127) / 128), dim3(128), 0, st, (const BT*)a,
+                                 lda, sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N,
+                                 K, out, ldo, scatter, limit));
+    return B200_OK;
+  }
+  dim3 grid(row_tiles, (N + GL_BN - 1) / GL_BN);
   B200_DISPATCH_ELEM(dtype, ET, {
     if (glu)
       B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_GLU>, grid, dim3(GL_THREADS), 0, st, (const ET*)a, lda, sorted_ids,
