@@ -716,8 +716,17 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: override the layer count (result is then NOT the headline)")
     ap.add_argument("--attn-traffic", type=float, default=None,
                     help="dram bytes read+written per attention launch from the committed ncu --set full capture")
+    ap.add_argument("--hybrid", default="", choices=["", "small", "1b", "all"],
+                    help="instead of the headline workload: prefill / decode throughput and per-kernel floors of the hybrid "
+                         "(state-space + windowed attention + MoE) decoder beside the dense decoder at equal size, one JSON "
+                         "line per size (vllm_neuron_b200/hybrid_bench.py)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.hybrid:
+        from vllm_neuron_b200 import hybrid_bench
+
+        args.steps = min(args.steps, 20)
+        return hybrid_bench.run(args)
     from dataclasses import replace
 
     from vllm_neuron_b200.config import PRESETS

@@ -313,7 +313,7 @@ int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w
                           void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
 /* Selective state-space scan: xbc [T][C] = [x: H*P | B: G*N | C: G*N] (x_dtype); dt_raw = dt_in[t][dt_col0 + h] (fp32);
  * dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x.
- * state fp32 [slots][H][N][P], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256. */
+ * state fp32 [slots][H][P][N], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256. */
 int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
                   const float* dt_bias, const float* D, float* state, const int32_t* seq_start, const int32_t* seq_slot,
                   const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, void* stream);
@@ -329,9 +329,16 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
                        int window, void* out, int T, int H, int G, int D, int Dv, int block_size, void* stream);
-/* Router: fp32 logits W_router h, sigmoid scores, the `top` largest (ties to the lower index); weights = chosen scores. */
-int b200_moe_router(const void* h, const void* w_router, int dtype, int32_t* topk_idx, float* topk_weight, int T, int W, int E,
-                    int top, void* stream);
+/* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
+ * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
+ * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32. */
+int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                               int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                               int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
+                               int Dv, int block_size, void* stream);
+/* Router decision over fp32 logits [T] rows of pitch ld: the `top` largest (ties to the lower index); weights = sigmoid of
+ * the chosen logits (no renormalisation). */
+int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_weight, int T, int E, int top, void* stream);
 /* rows per expert tile of b200_moe_align / b200_grouped_linear */
 int b200_moe_tile_rows(void);
 /* Sort the npairs (token, choice) pairs by expert into tiles: sorted_ids [cap] (pair id or -1), tile_expert [max_tiles],

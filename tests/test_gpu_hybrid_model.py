@@ -31,11 +31,12 @@ def cfg_a():
 
 
 def cfg_b():
-    """State-space first, groups == heads, two taps, top 1, width and sizes that keep every GEMM on the tensor-core path."""
+    """State-space first, groups == heads, two taps, top 1; every GEMM on the tensor-core path and head sizes (32 / 16) that
+    put prompt portions of 16 tokens or more on the tensor-core attention kernel."""
     return {"architecture": "Pumopel", "vocab": 200, "width": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5}, "layers": [
         _layer("mamba2", _moe(4, 1, 16, 1.5, 32), heads=4, vdim=8, state=8, groups=4, conv=2, norm_groups=2),
-        _layer("attention", _moe(4, 1, 16, 1.5, 32), heads=4, kv_heads=4, dim=16, vdim=8, scale=0.25, mask={"size": 40}, v_mix=True),
-        _layer("attention", None, heads=4, kv_heads=4, dim=16, vdim=8, scale=0.25, mask={"size": 5}, v_mix=True),
+        _layer("attention", _moe(4, 1, 16, 1.5, 32), heads=4, kv_heads=2, dim=32, vdim=16, scale=0.18, mask={"size": 40}, v_mix=True),
+        _layer("attention", None, heads=4, kv_heads=2, dim=32, vdim=16, scale=0.18, mask={"size": 5}, v_mix=True),
     ]}
 
 

@@ -118,7 +118,7 @@ def test_selective_scan_ragged(H, G, P, N):
         B = xbc[s][:, H * P:H * P + G * N].double().view(n, G, N).repeat_interleave(H // G, 1)
         Cm = xbc[s][:, H * P + G * N:].double().view(n, G, N).repeat_interleave(H // G, 1)
         want[s] = selective_scan(x, B, Cm, dts[s][:, 3:].double(), dt_bias.double(), a_log.double(), d.double()).reshape(n, H * P)
-    state = torch.full((3, H, N, P), 5.0, device=DEV)
+    state = torch.full((3, H, P, N), 5.0, device=DEV)
     plan = [[(0, 7), (1, 1)], [(0, 1), (1, 2), (2, 2)], [(0, 11), (2, 6)]]
     done = {s: 0 for s in lens}
     for step in plan:
@@ -191,6 +191,25 @@ def test_attention_window_edges_sink_and_pages(chunks):
     _close(_run_attn(q, k, v, sink, window, bs, chunks, torch.bfloat16), want, 3e-2)
 
 
+@pytest.mark.parametrize("chunks", [[150], [16, 64, 3, 67], [33, 1, 1, 17, 98]])
+def test_tensor_core_prompt_attention_edges(chunks):
+    """bf16 pools, head sizes 32 / 48: portions of 16 tokens or more run on the mma.sync kernel (64-row tiles, 32-key tiles
+    over pages of 8), shorter ones on the CUDA-core kernel.  A dominant key just inside / outside the window of a query in
+    the middle of a tile and of the last query, against the restatement on the bf16-rounded q / k / v."""
+    from oracle.pumopel_ref import sink_window_attention
+
+    T, H, G, D, Dv, window, bs = 150, 4, 2, 32, 48, 37, 8
+    for i in (T - 1, 100, 40):
+        for j, inside in ((i - window + 1, True), (i - window, False), (i, True)):
+            q, k, v, sink = _attn_case(T, H, G, D, Dv, window, bs, spike=(i, j, 3), seed=11)
+            qb, kb, vb = (x.bfloat16().float() for x in (q, k, v))
+            want = sink_window_attention(qb.double(), kb.double(), vb.double(), sink.double(), 1 / math.sqrt(D), window)
+            got = _run_attn(qb, kb, vb, sink, window, bs, chunks, torch.bfloat16)
+            _close(got, want, 1.5e-2)
+            head = got[i].float().view(H, Dv)[3].cpu()
+            assert ((head - vb[j, 3 // (H // G)]).abs().max() < 3e-2) == inside, (i, j)
+
+
 def test_far_key_among_hundreds_without_window():
     """No window: key 3 of 400 must still decide the last query (pages of 32)."""
     from oracle.pumopel_ref import sink_window_attention
@@ -242,7 +261,9 @@ def test_moe_weight_on_the_input(E, top, shared):
     W64 = {k: v.double() for k, v in Wt.items()}
     want = moe_ff(h.double(), W64, "l0.mlp.", cfgd["layers"][0]["mlp"])
     _close(got, want, 2e-5)
-    idx, wt = _ops().moe_router(h.to(DEV), model.layers[0]["w_router"], top)
+    idx, wt = _ops().moe_topk(model._linear(h.to(DEV), model.layers[0]["w_router"]), top)
+    ties = torch.tensor([[1.0, 3.0, 3.0, -2.0, 3.0]], device=DEV)            # equal logits: the lower index first
+    assert _ops().moe_topk(ties, 2)[0].tolist() == [[1, 2]]
     s = torch.sigmoid(h.double() @ W64["l0.mlp.router"].T)
     val, ref_idx = s.topk(top, dim=-1)
     assert torch.equal(idx.cpu().long(), ref_idx) and (wt.cpu().double() - val).abs().max() < 1e-6

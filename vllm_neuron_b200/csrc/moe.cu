@@ -1,6 +1,6 @@
 // Mixture-of-experts feed-forward over a token batch, and the generic grouped / dense linear kernel it is built on.
-//   * moe_router: logits = W_router h in fp32, score = sigmoid(logit); the `top` largest scores are chosen (ties go to the
-//     lower expert index) and the chosen SCORES are the routing weights (no renormalisation);
+//   * moe_topk: over the fp32 router logits (a linear of the layer's input): score = sigmoid(logit); the `top` largest are
+//     chosen (ties go to the lower expert index) and the chosen SCORES are the routing weights (no renormalisation);
 //   * moe_align: counting sort of the (token, choice) pairs by expert into row tiles of MOE_BM, each tile owned by one
 //     expert (ragged tails padded with -1), so the expert GEMMs run as one launch without the host knowing the counts;
 //   * grouped_linear: out = A W_e^T with fp32 accumulation over K in ascending order (the result of a row does not depend
@@ -18,50 +18,29 @@ constexpr int GL_BN = 64;
 constexpr int GL_BK = 16;
 constexpr int GL_THREADS = 256;
 
-template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ h, const T* __restrict__ wr, int W, int E, int top,
-                                  int32_t* __restrict__ idx, float* __restrict__ wt, int ntok) {
+// one thread per token: the `top` largest logits (ties to the lower index); weight = sigmoid(logit)
+__global__ void moe_topk_kernel(const float* __restrict__ z, int ld, int E, int top, int32_t* __restrict__ idx,
+                                float* __restrict__ wt, int ntok) {
   griddep_launch();
   griddep_wait();
-  extern __shared__ float zs_all[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= ntok) return;
-  float* z = zs_all + warp * E;
-  const T* hr = h + (int64_t)t * W;
-  for (int e = 0; e < E; ++e) {
-    const T* w = wr + (int64_t)e * W;
-    float acc = 0.f;
-    for (int i = lane; i < W; i += 32) acc += ldf(hr, i) * ldf(w, i);
-    acc = warp_sum(acc);
-    if (lane == 0) z[e] = acc;
-  }
-  __syncwarp();
+  const float* zr = z + (int64_t)t * ld;
+  int32_t* out = idx + (int64_t)t * top;
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
-      if (v > best || (v == best && e < bi)) {
+    int bi = -1;
+    for (int e = 0; e < E; ++e) {
+      bool taken = false;
+      for (int k = 0; k < c; ++k) taken |= out[k] == e;
+      const float v = zr[e];
+      if (!taken && (bi < 0 || v > best)) {
         best = v;
         bi = e;
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) {
-      idx[(int64_t)t * top + c] = bi;
-      wt[(int64_t)t * top + c] = 1.0f / (1.0f + expf(-best));
-      z[bi] = -INFINITY;
-    }
-    __syncwarp();
+    out[c] = bi;
+    wt[(int64_t)t * top + c] = 1.0f / (1.0f + expf(-best));
   }
 }
 
@@ -346,19 +325,12 @@ using namespace b200;
 
 extern "C" {
 
-int b200_moe_router(const void* h, const void* w_router, int dtype, int32_t* topk_idx, float* topk_weight, int T, int W, int E,
-                    int top, void* stream) {
-  B200_REQUIRE(h && w_router && topk_idx && topk_weight, "moe_router: null pointer");
-  B200_REQUIRE(E >= 1 && E <= 4096 && top >= 1 && top <= E, "moe_router: top %d of %d experts", top, E);
+int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_weight, int T, int E, int top, void* stream) {
+  B200_REQUIRE(logits && topk_idx && topk_weight, "moe_topk: null pointer");
+  B200_REQUIRE(E >= 1 && top >= 1 && top <= E && ld >= E, "moe_topk: top %d of %d experts", top, E);
   if (T <= 0) return B200_OK;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * 4;
-  B200_DISPATCH_ELEM(dtype, ET, {
-    if (smem > 48 * 1024)
-      B200_CUDA_OK(cudaFuncSetAttribute(moe_router_kernel<ET>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B200_CUDA_OK(launch_kernel(moe_router_kernel<ET>, dim3((T + warps - 1) / warps), dim3(warps * 32), smem, (cudaStream_t)stream,
-                               (const ET*)h, (const ET*)w_router, W, E, top, topk_idx, topk_weight, T));
-  });
+  B200_CUDA_OK(launch_kernel(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, logits, ld, E, top,
+                             topk_idx, topk_weight, T));
   return B200_OK;
 }
 

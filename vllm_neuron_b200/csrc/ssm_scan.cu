@@ -3,7 +3,7 @@
 //   * causal depthwise convolution + SiLU over the channels [x | B | C]; the last (taps - 1) inputs of a sequence are
 //     part of its state (fp32, [slots][taps - 1][channels], oldest first);
 //   * the selective scan  S_t = exp(-exp(A_log) dt_t) S_{t-1} + dt_t B_t x_t^T,  y_t = S_t^T C_t + D x_t  with
-//     dt_t = softplus(dt_raw + dt_bias), S in fp32 ([slots][heads][N][P]) and every term of the recurrence in fp32.
+//     dt_t = softplus(dt_raw + dt_bias), S in fp32 ([slots][heads][P][N]) and every term of the recurrence in fp32.
 // A sequence whose first new token is position 0 starts from zero state whatever its slot held before, so slots can be
 // handed to new requests without clearing them.
 #include "hybrid_common.cuh"
@@ -74,10 +74,14 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
 }
 
 // Selective scan.  CTA = (32 value columns p of one head) x (8 slices of the state dimension); thread (p, s) keeps
-// S[n][p] for n = s, s + 8, ... (NPT of them) in registers across the tokens of its sequence; y is reduced over the 8
-// slices with shuffles.  The next token's operands are fetched while the current one is applied.
+// S[p][n] for n = s, s + 8, ... (NPT of them) in registers across the tokens of its sequence; y is reduced over the 8
+// slices with shuffles.  The sequence is walked in chunks of SCAN_CHUNK tokens: the CTA stages the chunk's B, C and x rows
+// in shared memory with coalesced loads (fetched into registers one chunk ahead) and computes each token's step size and decay ONCE (softplus / exp are not
+// repeated by every thread), then the recurrence runs out of shared memory.  State layout [slots][H][P][N]: the 8 slices
+// of a column read consecutive floats.
 constexpr int SCAN_PCOLS = 32;
 constexpr int SCAN_SLICES = 8;
+constexpr int SCAN_CHUNK = 32;
 
 template <typename XT, int NPT>
 __global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
@@ -87,67 +91,96 @@ __global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
                     const int32_t* __restrict__ seq_pos0, float* __restrict__ y, int H, int P, int N, int G) {
   griddep_launch();
   griddep_wait();
-  const int h = blockIdx.y, sq = blockIdx.z;
-  const int s = threadIdx.x % SCAN_SLICES;
-  const int p = blockIdx.x * SCAN_PCOLS + threadIdx.x / SCAN_SLICES;
+  constexpr int NP = NPT * SCAN_SLICES;  // padded state size: rows of Bs / Cs
+  extern __shared__ float sm[];
+  float* Bs = sm;                               // [SCAN_CHUNK][NP]
+  float* Cs = Bs + SCAN_CHUNK * NP;             // [SCAN_CHUNK][NP]
+  float* xs = Cs + SCAN_CHUNK * NP;             // [SCAN_CHUNK][SCAN_PCOLS]
+  float* dts = xs + SCAN_CHUNK * SCAN_PCOLS;    // [SCAN_CHUNK]
+  float* dec = dts + SCAN_CHUNK;                // [SCAN_CHUNK]
+  const int h = blockIdx.y, sq = blockIdx.z, tid = threadIdx.x;
+  const int s = tid % SCAN_SLICES, pl = tid / SCAN_SLICES;
+  const int p0 = blockIdx.x * SCAN_PCOLS, p = p0 + pl;
   const bool pv = p < P;
-  const int pc = pv ? p : P - 1;
   const int g = h / (H / G);
   const int inner = H * P;
   const int t0 = seq_start[sq], t1 = seq_start[sq + 1];
-  float* S0 = state + (((int64_t)seq_slot[sq] * H + h) * N) * P + pc;
+  float* S0 = state + (((int64_t)seq_slot[sq] * H + h) * P + (pv ? p : 0)) * N;
   float S[NPT];
-  const bool cont = seq_pos0[sq] > 0;
+  const bool cont = seq_pos0[sq] > 0 && pv;
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
     const int n = s + i * SCAN_SLICES;
-    S[i] = (cont && n < N) ? S0[(int64_t)n * P] : 0.f;
+    S[i] = (cont && n < N) ? S0[n] : 0.f;
   }
   const float negA = -expf(A_log[h]), bias = dt_bias[h], dsk = Dskip[h];
-  const int64_t xcol = (int64_t)h * P + pc, bcol = (int64_t)inner + (int64_t)g * N, ccol = bcol + (int64_t)G * N;
-
-  float Bn[NPT], Cn[NPT], xv, dtr;
-  auto fetch = [&](int t) {
-    const XT* row = xbc + (int64_t)t * C;
-    xv = ldf(row, xcol);
-    dtr = dt_in[(int64_t)t * ld_dt + dt_col0 + h];
+  const int64_t xcol = (int64_t)h * P + p0, bcol = (int64_t)inner + (int64_t)g * N, ccol = bcol + (int64_t)G * N;
+  // global -> registers -> shared memory: the next chunk's loads are in flight while the current chunk is applied
+  constexpr int NTHR = SCAN_PCOLS * SCAN_SLICES;
+  constexpr int BC_PER = SCAN_CHUNK * NP / NTHR;
+  constexpr int X_PER = SCAN_CHUNK * SCAN_PCOLS / NTHR;
+  float rB[BC_PER], rC[BC_PER], rx[X_PER], rdt = 0.f;
+  auto fetch = [&](int c0) {
+    const int nc = t1 - c0 < SCAN_CHUNK ? t1 - c0 : SCAN_CHUNK;
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int n = s + i * SCAN_SLICES;
-      Bn[i] = n < N ? ldf(row, bcol + n) : 0.f;
-      Cn[i] = n < N ? ldf(row, ccol + n) : 0.f;
+    for (int k = 0; k < BC_PER; ++k) {
+      const int i = tid + k * NTHR, tok = i / NP, n = i - tok * NP;
+      const bool in = tok < nc && n < N;
+      const XT* row = xbc + (int64_t)(c0 + (tok < nc ? tok : 0)) * C;
+      rB[k] = in ? ldf(row, bcol + n) : 0.f;
+      rC[k] = in ? ldf(row, ccol + n) : 0.f;
     }
+#pragma unroll
+    for (int k = 0; k < X_PER; ++k) {
+      const int i = tid + k * NTHR, tok = i / SCAN_PCOLS, pp = i - tok * SCAN_PCOLS;
+      rx[k] = (tok < nc && p0 + pp < P) ? ldf(xbc + (int64_t)(c0 + tok) * C, xcol + pp) : 0.f;
+    }
+    if (tid < nc) rdt = dt_in[(int64_t)(c0 + tid) * ld_dt + dt_col0 + h];
   };
   if (t0 < t1) fetch(t0);
-  for (int t = t0; t < t1; ++t) {
-    float Bc[NPT], Cc[NPT];
-    const float xc = xv, dtc = dtr;
+  for (int c0 = t0; c0 < t1; c0 += SCAN_CHUNK) {
+    const int nc = t1 - c0 < SCAN_CHUNK ? t1 - c0 : SCAN_CHUNK;
+    __syncthreads();  // the previous chunk has been consumed
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      Bc[i] = Bn[i];
-      Cc[i] = Cn[i];
+    for (int k = 0; k < BC_PER; ++k) {
+      Bs[tid + k * NTHR] = rB[k];
+      Cs[tid + k * NTHR] = rC[k];
     }
-    if (t + 1 < t1) fetch(t + 1);
-    const float z = dtc + bias;
-    const float dt = z > 20.f ? z : log1pf(expf(z));  // softplus, no clamp on the step size
-    const float a = expf(negA * dt);
-    const float dx = dt * xc;
-    float acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      S[i] = a * S[i] + Bc[i] * dx;
-      acc += S[i] * Cc[i];
+    for (int k = 0; k < X_PER; ++k) xs[tid + k * NTHR] = rx[k];
+    if (tid < nc) {
+      const float z = rdt + bias;
+      const float dt = z > 20.f ? z : log1pf(expf(z));  // softplus, no clamp on the step size
+      dts[tid] = dt;
+      dec[tid] = expf(negA * dt);
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-    if (s == 0 && pv) y[(int64_t)t * inner + xcol] = acc + dsk * xc;
+    __syncthreads();
+    if (c0 + SCAN_CHUNK < t1) fetch(c0 + SCAN_CHUNK);
+    for (int tok = 0; tok < nc; ++tok) {
+      const float xc = xs[tok * SCAN_PCOLS + pl];
+      const float a = dec[tok], dx = dts[tok] * xc;
+      const float* Br = Bs + tok * NP + s;
+      const float* Cr = Cs + tok * NP + s;
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; i += 2) {
+        S[i] = a * S[i] + Br[i * SCAN_SLICES] * dx;
+        acc0 += S[i] * Cr[i * SCAN_SLICES];
+        S[i + 1] = a * S[i + 1] + Br[(i + 1) * SCAN_SLICES] * dx;
+        acc1 += S[i + 1] * Cr[(i + 1) * SCAN_SLICES];
+      }
+      float acc = acc0 + acc1;
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (s == 0 && pv) y[(int64_t)(c0 + tok) * inner + xcol + pl] = acc + dsk * xc;
+    }
   }
   if (pv) {
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
       const int n = s + i * SCAN_SLICES;
-      if (n < N) S0[(int64_t)n * P] = S[i];
+      if (n < N) S0[n] = S[i];
     }
   }
 }
@@ -157,7 +190,10 @@ static int launch_scan(const void* xbc, int C, const float* dt_in, int ld_dt, in
                        const float* dt_bias, const float* Dskip, float* state, const int32_t* seq_start, const int32_t* seq_slot,
                        const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, cudaStream_t stream) {
   dim3 grid((P + SCAN_PCOLS - 1) / SCAN_PCOLS, H, B);
-  B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT>, grid, dim3(SCAN_PCOLS * SCAN_SLICES), 0, stream, (const XT*)xbc, C, dt_in,
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * NPT * SCAN_SLICES + SCAN_PCOLS + 2)) * sizeof(float);
+  if (smem > 48 * 1024)
+    B200_CUDA_OK(cudaFuncSetAttribute(ssd_scan_kernel<XT, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT>, grid, dim3(SCAN_PCOLS * SCAN_SLICES), smem, stream, (const XT*)xbc, C, dt_in,
                              ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y, H, P, N, G));
   return B200_OK;
 }

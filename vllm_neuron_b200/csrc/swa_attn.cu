@@ -3,7 +3,7 @@
 //   * kv_write_vmix: scatters this step's keys and values into the pools by slot; optionally mixes the value with the
 //     value the first value-mixing layer produced for the same token, v + lambda (v_first - v), BEFORE it is
 //     cached (what is cached is what every later query reads);
-//   * swa_sink_attn: ragged batch, one warp per (token, query head).  A query at position i attends keys i - window < j <= i,
+//   * swa_sink_attn: ragged batch, one CTA per (token, query head).  A query at position i attends keys i - window < j <= i,
 //     read through the sequence's block table.  Online softmax in fp32 that STARTS from the sink: running maximum =
 //     sink logit, running denominator = 1, accumulator = 0 -- the sink adds exp(sink) to the denominator once, has no key,
 //     no value, and is not multiplied by the score scale.
@@ -40,6 +40,54 @@ __global__ void kv_write_vmix_kernel(const float* __restrict__ qkv, int ld, int 
 
 constexpr int ATT_WARPS = 4;
 
+// q (fp32, shared memory) . k row, with 16-byte loads when the row allows it
+template <typename KT>
+__device__ __forceinline__ float dot_q_row(const float* __restrict__ qs, const KT* __restrict__ kr, int D);
+template <>
+__device__ __forceinline__ float dot_q_row<float>(const float* __restrict__ qs, const float* __restrict__ kr, int D) {
+  float dot = 0.f;
+  if ((D & 3) == 0) {
+    for (int d = 0; d < D; d += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
+      dot += qs[d] * k4.x + qs[d + 1] * k4.y + qs[d + 2] * k4.z + qs[d + 3] * k4.w;
+    }
+  } else {
+    for (int d = 0; d < D; ++d) dot += qs[d] * kr[d];
+  }
+  return dot;
+}
+template <>
+__device__ __forceinline__ float dot_q_row<__nv_bfloat16>(const float* __restrict__ qs, const __nv_bfloat16* __restrict__ kr, int D) {
+  float dot = 0.f;
+  if ((D & 7) == 0) {
+    for (int d = 0; d < D; d += 8) {
+      const uint4 k8 = *reinterpret_cast<const uint4*>(kr + d);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&k8);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        dot += qs[d + 2 * i] * f.x + qs[d + 2 * i + 1] * f.y;
+      }
+    }
+  } else {
+    for (int d = 0; d < D; ++d) dot += qs[d] * __bfloat162float(kr[d]);
+  }
+  return dot;
+}
+// two consecutive elements of a value row (pairs: lane l owns columns 2 l, 2 l + 1 of every 64-column slab)
+__device__ __forceinline__ float2 ld_pair(const float* r, int d, int Dv, bool vec) {
+  if (vec) return *reinterpret_cast<const float2*>(r + d);
+  return make_float2(d < Dv ? r[d] : 0.f, d + 1 < Dv ? r[d + 1] : 0.f);
+}
+__device__ __forceinline__ float2 ld_pair(const __nv_bfloat16* r, int d, int Dv, bool vec) {
+  if (vec) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(r + d));
+  return make_float2(d < Dv ? __bfloat162float(r[d]) : 0.f, d + 1 < Dv ? __bfloat162float(r[d + 1]) : 0.f);
+}
+
+// One CTA per (token, query head): its 4 warps take the window's 32-key tiles round-robin (lane-per-key scores,
+// lanes-over-columns value accumulation, each warp its own running maximum / denominator / accumulator) and merge through
+// shared memory.  Warp 0 carries the sink's 1 in the denominator.  The split depends on the position and the window only.
+// Serves decoded tokens and short portions in both element types, and every shape in 32-bit serving.
 template <typename KT, int MAXC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
     swa_sink_attn_kernel(const float* __restrict__ q, int ldq, const KT* __restrict__ k_pool, const KT* __restrict__ v_pool,
@@ -48,41 +96,42 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                          KT* __restrict__ out, int T, int H, int G, int D, int Dv, int bs) {
   griddep_launch();
   griddep_wait();
-  extern __shared__ float qs_all[];
+  extern __shared__ float sm_att[];
+  float* qs = sm_att;                      // [D]
+  float* accs = qs + D;                    // [ATT_WARPS][64 MAXC]
+  float* ml = accs + ATT_WARPS * 64 * MAXC;  // [ATT_WARPS][2]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t pair = (int64_t)blockIdx.x * ATT_WARPS + warp;
-  if (pair >= (int64_t)T * H) return;
-  const int t = (int)(pair / H), h = (int)(pair - (int64_t)t * H);
+  const int t = blockIdx.x / H, h = blockIdx.x - t * H;
   const int g = h / (H / G);
-  float* qs = qs_all + warp * D;
-  for (int d = lane; d < D; d += 32) qs[d] = q[(int64_t)t * ldq + (int64_t)h * D + d];
-  __syncwarp();
+  for (int d = threadIdx.x; d < D; d += ATT_WARPS * 32) qs[d] = q[(int64_t)t * ldq + (int64_t)h * D + d];
+  __syncthreads();
   const int pos = tok_pos[t];
   const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
   const int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
-  float m = sink[h], l = 1.0f;  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
-  float acc[MAXC];
+  const bool vvec = (Dv & 1) == 0;
+  float m = sink[h], l = warp == 0 ? 1.0f : 0.f;  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
+  float2 acc[MAXC];
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c) acc[c] = 0.f;
-  for (int j0 = lo; j0 <= pos; j0 += 32) {
+  for (int c = 0; c < MAXC; ++c) acc[c] = make_float2(0.f, 0.f);
+  for (int j0 = lo + 32 * warp; j0 <= pos; j0 += 32 * ATT_WARPS) {
     const int j = j0 + lane;
     const bool valid = j <= pos;
-    int64_t tile = 0;  // element offset of (block, kv head, token) row 0 in units of one row
+    int64_t tile = 0;  // row index of (block, kv head, token) in the pools
     float s = -INFINITY;
     if (valid) {
       const int64_t blk = bt[j / bs];
       tile = (blk * G + g) * bs + (j % bs);
-      const KT* kr = k_pool + tile * D;
-      float dot = 0.f;
-      for (int d = 0; d < D; ++d) dot += qs[d] * ldf(kr, d);
-      s = dot * scale;
+      s = dot_q_row(qs, k_pool + tile * D, D) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);
     const float p = valid ? expf(s - m_new) : 0.f;
     l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int c = 0; c < MAXC; ++c) acc[c] *= corr;
+    for (int c = 0; c < MAXC; ++c) {
+      acc[c].x *= corr;
+      acc[c].y *= corr;
+    }
     m = m_new;
     const int cnt = pos - j0 + 1 < 32 ? pos - j0 + 1 : 32;
     for (int jj = 0; jj < cnt; ++jj) {
@@ -91,16 +140,42 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       const KT* vr = v_pool + tj * Dv;
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
-        const int d = lane + 32 * c;
-        if (d < Dv) acc[c] += pj * ldf(vr, d);
+        const int d = 2 * lane + 64 * c;
+        if (d < Dv) {
+          const float2 v2 = ld_pair(vr, d, Dv, vvec);
+          acc[c].x += pj * v2.x;
+          acc[c].y += pj * v2.y;
+        }
       }
     }
   }
-  const float inv = 1.0f / l;
+  // ---- merge the warps (fixed order 0..3)
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
-    const int d = lane + 32 * c;
-    if (d < Dv) stf(out, ((int64_t)t * H + h) * Dv + d, acc[c] * inv);
+    accs[(warp * MAXC + c) * 64 + 2 * lane] = acc[c].x;
+    accs[(warp * MAXC + c) * 64 + 2 * lane + 1] = acc[c].y;
+  }
+  if (lane == 0) {
+    ml[2 * warp] = m;
+    ml[2 * warp + 1] = l;
+  }
+  __syncthreads();
+  float mt = ml[0];
+#pragma unroll
+  for (int w = 1; w < ATT_WARPS; ++w) mt = fmaxf(mt, ml[2 * w]);
+  float lt = 0.f, f[ATT_WARPS];
+#pragma unroll
+  for (int w = 0; w < ATT_WARPS; ++w) {
+    f[w] = expf(ml[2 * w] - mt);
+    lt += ml[2 * w + 1] * f[w];
+  }
+  const float inv = 1.0f / lt;
+  for (int d = threadIdx.x; d < Dv; d += ATT_WARPS * 32) {
+    const int c = d >> 6, e = d & 63;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) v += accs[(w * MAXC + c) * 64 + e] * f[w];
+    stf(out, ((int64_t)t * H + h) * Dv + d, v * inv);
   }
 }
 
@@ -131,18 +206,18 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   B200_REQUIRE(window >= 1, "swa_sink_attn: window %d", window);
   B200_REQUIRE(Dv >= 1 && Dv <= 256 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..256", D, Dv);
   if (T <= 0) return B200_OK;
-  const int64_t pairs = (int64_t)T * H;
-  dim3 grid((unsigned)((pairs + ATT_WARPS - 1) / ATT_WARPS));
-  const size_t smem = (size_t)ATT_WARPS * D * 4;
+  B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
+  dim3 grid((unsigned)(T * H));
   cudaStream_t st = (cudaStream_t)stream;
 #define ATT_LAUNCH(MC)                                                                                                      \
-  B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq, (const KT*)k_pool, \
+  B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC>, grid, dim3(ATT_WARPS * 32),                                      \
+                             (size_t)(D + ATT_WARPS * 64 * MC + 2 * ATT_WARPS) * 4, st, q, ldq, (const KT*)k_pool,         \
                              (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, window, (KT*)out, T, H, G, \
                              D, Dv, block_size))
   B200_DISPATCH_ELEM(kv_dtype, KT, {
-    if (Dv <= 64) ATT_LAUNCH(2);
-    else if (Dv <= 128) ATT_LAUNCH(4);
-    else ATT_LAUNCH(8);
+    if (Dv <= 64) ATT_LAUNCH(1);
+    else if (Dv <= 128) ATT_LAUNCH(2);
+    else ATT_LAUNCH(4);
   });
 #undef ATT_LAUNCH
   return B200_OK;

@@ -1,0 +1,210 @@
+// Tensor-core prompt-portion kernel of the sliding-window sink attention (bf16 pools): same contract as swa_sink_attn in
+// swa_attn.cu -- a query at position i attends keys i - window < j <= i through its block table, the softmax starts
+// from the per-head sink (running maximum = sink, denominator = 1, no value) -- computed FlashAttention-style.
+//   CTA = 64 consecutive new tokens of one sequence x one query head, 4 warps x 16 rows.  Keys are walked in tiles of 32
+//   from the first key the tile's first row may see to the last key its last row may see; each tile's K and V rows are
+//   gathered page by page into shared memory (rows padded by 16 bytes: conflict-free ldmatrix), S = Q K^T and O += P V run
+//   on mma.sync m16n8k16 (bf16 in, fp32 accumulate); the mask is applied per element, the online softmax is fp32.
+// Needs D % 16 == 0 and Dv % 16 == 0, Dv <= 256; other shapes, fp32 pools and decode-sized steps use the warp kernel.
+#include <math.h>
+
+#include "hybrid_common.cuh"
+
+namespace b200 {
+
+constexpr int PF_ROWS = 64;
+constexpr int PF_KEYS = 32;
+
+template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
+__global__ void __launch_bounds__(128)
+    swa_sink_prefill_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
+                            const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
+                            const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                            const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
+                            __nv_bfloat16* __restrict__ out, int H, int G, int D, int Dv, int bs) {
+  griddep_launch();
+  griddep_wait();
+  const int sq = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PF_ROWS;
+  const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
+  if (i0 >= n) return;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int ldk = D + 8, ldv = Dv + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [64][ldk]
+  __nv_bfloat16* Ks = Qs + PF_ROWS * ldk;                       // [32][ldk]
+  __nv_bfloat16* Vs = Ks + PF_KEYS * ldk;                       // [32][ldv]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = h / (H / G);
+  const int pos0 = seq_pos0[sq];
+  const int32_t* bt = block_table + (int64_t)seq_slot[sq] * bt_stride;
+  // ---- Q tile: fp32 rows -> bf16 shared memory (rows past the portion are zero)
+  for (int i = tid; i < PF_ROWS * (D / 2); i += 128) {
+    const int r = i / (D / 2), d = (i - r * (D / 2)) * 2;
+    float2 v = make_float2(0.f, 0.f);
+    if (i0 + r < n) v = *reinterpret_cast<const float2*>(q + (int64_t)(t0 + i0 + r) * ldq + (int64_t)h * D + d);
+    *reinterpret_cast<__nv_bfloat162*>(Qs + r * ldk + d) = __floats2bfloat162_rn(v.x, v.y);
+  }
+  // rows of this thread's accumulators: r_lo = 16 warp + lane / 4, r_hi = r_lo + 8
+  const int r_lo = 16 * warp + (lane >> 2);
+  const int p_lo = pos0 + i0 + r_lo, p_hi = p_lo + 8;
+  const bool ok_lo = i0 + r_lo < n, ok_hi = i0 + r_lo + 8 < n;
+  float m_lo = sink[h], m_hi = m_lo;
+  float l_lo = (lane & 3) == 0 ? 1.0f : 0.f, l_hi = l_lo;  // the sink's share of the denominator, counted once per row
+  float o[2 * DV16M][4];
+#pragma unroll
+  for (int j = 0; j < 2 * DV16M; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
+  const int first_pos = pos0 + i0;
+  const int last_row = (n - i0 < PF_ROWS ? n - i0 : PF_ROWS) - 1;
+  const int j_lo = first_pos - window + 1 > 0 ? first_pos - window + 1 : 0;
+  const int j_hi = first_pos + last_row;  // inclusive
+  const int kch = D / 8, vch = Dv / 8;    // 16-byte chunks per row
+  for (int j0 = (j_lo / PF_KEYS) * PF_KEYS; j0 <= j_hi; j0 += PF_KEYS) {
+    __syncthreads();  // everyone is done with the previous tile (and, first time, Q is written)
+    for (int i = tid; i < PF_KEYS * (kch + vch); i += 128) {
+      const int r = i / (kch + vch), c = i - r * (kch + vch);
+      const int j = j0 + r;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      int64_t row = -1;
+      if (j <= j_hi) row = ((int64_t)bt[j / bs] * G + g) * bs + (j % bs);
+      if (c < kch) {
+        if (row >= 0) val = *reinterpret_cast<const uint4*>(k_pool + row * D + c * 8);
+        *reinterpret_cast<uint4*>(Ks + r * ldk + c * 8) = val;
+      } else {
+        if (row >= 0) val = *reinterpret_cast<const uint4*>(v_pool + row * Dv + (c - kch) * 8);
+        *reinterpret_cast<uint4*>(Vs + r * ldv + (c - kch) * 8) = val;
+      }
+    }
+    __syncthreads();
+    // ---- S = Q K^T: 16 rows x 32 keys per warp
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+    for (int kk = 0; kk < D; kk += 16) {
+      uint32_t af[4];
+      ldmatrix_x4(af, smem_u32(Qs + (16 * warp + (lane & 15)) * ldk + kk + (lane >> 4) * 8));
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        uint32_t bf[4];
+        const int mi = lane >> 3;
+        ldmatrix_x4(bf, smem_u32(Ks + (16 * jp + (mi >> 1) * 8 + (lane & 7)) * ldk + kk + (mi & 1) * 8));
+        mma_bf16_16816(s[2 * jp], af, bf[0], bf[1]);
+        mma_bf16_16816(s[2 * jp + 1], af, bf[2], bf[3]);
+      }
+    }
+    // ---- mask, online softmax (fp32)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = j0 + 8 * j + 2 * (lane & 3) + (c & 1);
+        const bool hi = c >= 2;
+        const int pos = hi ? p_hi : p_lo;
+        const bool seen = (hi ? ok_hi : ok_lo) && key <= pos && pos - key < window;
+        const float v = seen ? s[j][c] * scale : -INFINITY;
+        s[j][c] = v;
+        if (hi) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
+      }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float c_lo = __expf(m_lo - mn_lo), c_hi = __expf(m_hi - mn_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= c_lo;
+    l_hi *= c_hi;
+    uint32_t pf[4][2];  // P as bf16 pairs: [n8 tile][row half]
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p0 = __expf(s[j][0] - mn_lo), p1 = __expf(s[j][1] - mn_lo);
+      const float p2 = __expf(s[j][2] - mn_hi), p3 = __expf(s[j][3] - mn_hi);
+      l_lo += p0 + p1;
+      l_hi += p2 + p3;
+      pf[j][0] = pack_bf16(p0, p1);
+      pf[j][1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int j = 0; j < 2 * DV16M; ++j) {
+      o[j][0] *= c_lo;
+      o[j][1] *= c_lo;
+      o[j][2] *= c_hi;
+      o[j][3] *= c_hi;
+    }
+    // ---- O += P V: keys are the contraction (two k16 steps), V rows read transposed
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const uint32_t af[4] = {pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1]};
+#pragma unroll
+      for (int jd = 0; jd < DV16M; ++jd) {
+        if (jd * 16 < Dv) {
+          uint32_t bf[4];
+          const int mi = lane >> 3;
+          ldmatrix_x4_trans(bf, smem_u32(Vs + (16 * ks + (mi & 1) * 8 + (lane & 7)) * ldv + jd * 16 + (mi >> 1) * 8));
+          mma_bf16_16816(o[2 * jd], af, bf[0], bf[1]);
+          mma_bf16_16816(o[2 * jd + 1], af, bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+#pragma unroll
+  for (int j = 0; j < 2 * DV16M; ++j) {
+    const int d = 8 * j + 2 * (lane & 3);
+    if (d < Dv) {
+      if (ok_lo)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t)(t0 + i0 + r_lo) * H + h) * Dv + d) =
+            __floats2bfloat162_rn(o[j][0] * inv_lo, o[j][1] * inv_lo);
+      if (ok_hi)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t)(t0 + i0 + r_lo + 8) * H + h) * Dv + d) =
+            __floats2bfloat162_rn(o[j][2] * inv_hi, o[j][3] * inv_hi);
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                               int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                               int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
+                               int Dv, int block_size, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && seq_start && seq_slot && seq_pos0 && sink && out,
+               "swa_sink_attn_prefill: null pointer");
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1, "swa_sink_attn_prefill: %d query heads over %d kv heads", H, G);
+  if (D % 16 || Dv % 16 || Dv > 256 || D > 512 || (ldq & 1) || ((uintptr_t)q & 7)) {
+    set_last_error("swa_sink_attn_prefill: head sizes %d / %d need multiples of 16 (<= 512 / 256)", D, Dv);
+    return B200_ERR_UNSUPPORTED;
+  }
+  if (B <= 0 || max_new <= 0) return B200_OK;
+  dim3 grid((max_new + PF_ROWS - 1) / PF_ROWS, H, B);
+  const size_t smem = ((size_t)(PF_ROWS + PF_KEYS) * (D + 8) + (size_t)PF_KEYS * (Dv + 8)) * 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  typedef __nv_bfloat16 BT;
+#define PF_LAUNCH(M)                                                                                                          \
+  do {                                                                                                                        \
+    if (smem > 48 * 1024)                                                                                                     \
+      B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(128), smem, st, q, ldq, (const BT*)k_pool,              \
+                               (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
+                               (BT*)out, H, G, D, Dv, block_size));                                                           \
+  } while (0)
+  if (Dv <= 64) PF_LAUNCH(4);
+  else if (Dv <= 128) PF_LAUNCH(8);
+  else PF_LAUNCH(16);
+#undef PF_LAUNCH
+  return B200_OK;
+}
+
+}  // extern "C"

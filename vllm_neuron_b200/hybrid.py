@@ -229,6 +229,7 @@ class StepMeta:
     tok_row: torch.Tensor
     tok_pos: torch.Tensor
     slot_mapping: torch.Tensor  # int64 [T]: KV slot = block id * block_size + offset
+    max_new: int = 0            # longest portion of the step (host)
 
     @staticmethod
     def build(entries, block_rows, block_size: int, device) -> "StepMeta":
@@ -262,7 +263,7 @@ class StepMeta:
         for a in parts:
             cut.append(dev[o:o + a.size])
             o += a.size
-        return StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64))
+        return StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64), int(n.max()) if b else 0)
 
 
 # ------------------------------------------------------------------------------------------------ the model
@@ -315,7 +316,7 @@ class HybridCausalLM:
                           dt_bias=vec(p + "mix.dt_bias"), a_log=vec(p + "mix.A_log"), d=vec(p + "mix.D"),
                           gnorm=vec(p + "mix.norm"), w_o=lin(p + "mix.o"),
                           conv_state=torch.zeros((slots, m.conv - 1, m.channels), dtype=torch.float32, device=dev),
-                          ssm_state=torch.zeros((slots, m.heads, m.state, m.vdim), dtype=torch.float32, device=dev))
+                          ssm_state=torch.zeros((slots, m.heads, m.vdim, m.state), dtype=torch.float32, device=dev))
             else:
                 lw.update(w_qkv=lin(p + "mix.q", p + "mix.k", p + "mix.v"), sink=vec(p + "mix.sink"), w_o=lin(p + "mix.o"),
                           k_pool=torch.zeros((num_blocks, m.kv_heads, block_size, m.dim), dtype=et, device=dev),
@@ -358,8 +359,10 @@ class HybridCausalLM:
     # ------------------------------------------------------------------ building blocks
     def _linear(self, a, w):
         """fp32 [M, N] = a @ w^T.  bf16 serving: the tcgen05 GEMM (TMA needs K * 2 bytes to be a multiple of 16); anything
-        else, and all of 32-bit serving, runs on the CUDA cores with true fp32 arithmetic."""
-        if self.et == torch.bfloat16 and w.shape[1] % 8 == 0:
+        else, and all of 32-bit serving, runs on the CUDA cores with true fp32 arithmetic.  A prompt-sized batch against a
+        very narrow weight (the router) would leave the 128-row tcgen05 weight tile almost empty: it takes the mma.sync
+        kernel behind linear_simt instead."""
+        if self.et == torch.bfloat16 and w.shape[1] % 8 == 0 and not (w.shape[0] <= 32 and a.shape[0] > 128):
             m, (n, k) = a.shape[0], w.shape
             need = ops.gemm_workspace_bytes(m, n, k, ops.BF16, 0)
             if need and (self.gemm_ws is None or self.gemm_ws.numel() < need):
@@ -391,7 +394,7 @@ class HybridCausalLM:
 
     def _moe(self, lw, h):
         f = lw["spec"].mlp
-        idx, wt = ops.moe_router(h, lw["w_router"], f.top)
+        idx, wt = ops.moe_topk(self._linear(h, lw["w_router"]), f.top)  # fp32 logits, sigmoid scores
         pairs = ops.moe_experts(h, wt, ops.moe_align(idx, f.experts), lw["w_gu"], lw["w_down"], f.top, f.limit)
         shared = None
         if f.shared_ff:

@@ -1,0 +1,199 @@
+"""Prefill / decode throughput of the hybrid decoder next to the dense Llama decoder at equal size (bench.py --hybrid).
+
+For each size: random weights, both models in bf16 on one GPU, same width / layer count / vocabulary; the dense model's
+intermediate size equals the hybrid's ACTIVE feed-forward width (top * ff + shared ff) so a token costs about the same FLOPs.
+  prefill : one prompt of S tokens in one step                       -> tokens/s
+  decode  : B sequences holding `ctx` tokens each, one token apiece  -> tokens/s
+Timed with CUDA events around each step (eager launches, L2 flushed between steps, >= 3 warm-ups).  A second, untimed pass
+records every kernel with CUDA events (ops.kernel_timer) and sets it against its own floor: max(FLOPs / measured bf16 GEMM
+peak, algorithmic bytes / measured copy bandwidth), both from MEASURED_PEAKS.json.  One JSON line per size.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+
+import torch
+
+from . import ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# width, layers, then the mixers / feed-forward of the hybrid; layer pattern 'm m a m' repeated
+SIZES = {
+    "1b": dict(width=2048, layers=8, vocab=32000, ssm=dict(heads=32, vdim=128, state=128, groups=8, conv=4, norm_groups=8),
+               attn=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024),
+               moe=dict(experts=16, top=2, ff=1024, shared=2048), prefill=4096, batch=64, ctx=2048),
+    "small": dict(width=1024, layers=8, vocab=32000, ssm=dict(heads=32, vdim=64, state=64, groups=4, conv=4, norm_groups=4),
+                  attn=dict(heads=16, kv_heads=4, dim=64, vdim=64, window=512),
+                  moe=dict(experts=8, top=2, ff=512, shared=1024), prefill=2048, batch=32, ctx=1024),
+}
+
+
+def hybrid_config(sz: dict):
+    from .hybrid import HybridConfig
+
+    a, s, m = sz["attn"], sz["ssm"], sz["moe"]
+    mlp = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"], "limit": 7.0},
+           "shared": {"ff": m["shared"], "limit": 7.0}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {"heads": a["heads"], "kv_heads": a["kv_heads"], "dim": a["dim"],
+                                                     "vdim": a["vdim"], "scale": a["dim"] ** -0.5, "mask": {"size": a["window"]},
+                                                     "v_mix": True}}
+    ssm = {"type": "mamba2", "mlp": mlp, "mixer": dict(s)}
+    layers = [att if i % 4 == 2 else ssm for i in range(sz["layers"])]
+    return HybridConfig.from_dict({"architecture": "Pumopel", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-6},
+                                   "embedding": {"scale": 1.0}, "layers": layers})
+
+
+def dense_shape(sz: dict):
+    from .config import ModelShape
+
+    m = sz["moe"]
+    return ModelShape(f"dense-{sz['width']}", sz["width"], sz["layers"], sz["width"] // 128, max(1, sz["width"] // 512), 128,
+                      m["top"] * m["ff"] + m["shared"], sz["vocab"])
+
+
+def _peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"] * 1e9, p["bf16_tflops"] * 1e12, "measured"
+    except Exception:
+        return 6.65e12, 1.59e15, "fallback"
+
+
+def _timed(fn, steps, warmup, flush):
+    for _ in range(max(3, warmup)):
+        fn()
+    ms = []
+    for _ in range(steps):
+        flush.fill_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    ms.sort()
+    return ms[len(ms) // 2]
+
+
+def _floors(cfg, sz, t, keys_per_query, kv_tokens, nseq):
+    """Algorithmic (flops, bytes) per launch of the hybrid decoder's own kernels at `t` tokens."""
+    a, s, m, w = sz["attn"], sz["ssm"], sz["moe"], sz["width"]
+    inner, c = s["heads"] * s["vdim"], s["heads"] * s["vdim"] + 2 * s["groups"] * s["state"]
+    pairs = t * m["top"]
+    used = min(m["experts"], pairs)
+    att = (2.0 * t * a["heads"] * keys_per_query * (a["dim"] + a["vdim"]),
+           2.0 * kv_tokens * a["kv_heads"] * (a["dim"] + a["vdim"]) + t * a["heads"] * (4 * a["dim"] + 2 * a["vdim"]))
+    return {
+        "swa_sink_attn_prefill": att,
+        "swa_sink_attn": (2.0 * t * a["heads"] * keys_per_query * (a["dim"] + a["vdim"]),
+                          2.0 * kv_tokens * a["kv_heads"] * (a["dim"] + a["vdim"]) + t * a["heads"] * (4 * a["dim"] + 2 * a["vdim"])),
+        "ssd_scan": (6.0 * t * s["heads"] * s["state"] * s["vdim"],
+                     t * (2 * c + 4 * s["heads"] + 4 * inner) + 8.0 * nseq * s["heads"] * s["state"] * s["vdim"]),
+        "moe_gate_up_glu": (4.0 * pairs * m["ff"] * w, used * 4.0 * m["ff"] * w + t * 2 * w + pairs * 2 * m["ff"]),
+        "moe_down": (2.0 * pairs * m["ff"] * w, used * 2.0 * m["ff"] * w + pairs * (2 * m["ff"] + 4 * w)),
+        "causal_conv_silu": (0.0, t * (4 * c + 2 * c)),
+        "gated_group_rmsnorm": (0.0, t * inner * 10.0),
+        "dyt_residual": (0.0, t * w * (4 + 4 + 4 + 2.0)),
+        "kv_write_vmix": (0.0, t * a["kv_heads"] * (a["dim"] + a["vdim"]) * 6.0),
+        "clamped_glu": (0.0, t * m["shared"] * 10.0),
+    }
+
+
+def _gemm_floor(name):
+    g = re.match(r"(gemm\w*|linear_simt)\[(\d+)x(\d+)x(\d+)\]", name)
+    if not g:
+        return None
+    mm, n, k = int(g.group(2)), int(g.group(3)), int(g.group(4))
+    return 2.0 * mm * n * k, 2.0 * (mm * k + n * k) + 4.0 * mm * n
+
+
+def _breakdown(fn, floors, hbm, peak):
+    with ops.kernel_timer() as kt:
+        fn()
+    out = {}
+    for name, (cnt, ms) in sorted(kt.summary().items(), key=lambda kv: -kv[1][0] * kv[1][1]):
+        fb = _gemm_floor(name) or floors.get(name)
+        row = {"launches": cnt, "ms": round(ms, 4)}
+        if fb:
+            floor_ms = max(fb[0] / peak, fb[1] / hbm) * 1e3
+            row.update(floor_ms=round(floor_ms, 5), frac_of_floor=round(floor_ms / ms, 4) if ms > 0 else None)
+        out[name] = row
+    return out
+
+
+def run(args):
+    from .hybrid import HybridCausalLM, StepMeta
+    from .model import B200CausalLM
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    hbm, peak, src = _peaks()
+    flush = torch.empty(192 << 20, dtype=torch.float32, device=dev)  # 768 MB > L2
+    names = list(SIZES) if args.hybrid == "all" else [args.hybrid]
+    for name in names:
+        sz = SIZES[name]
+        cfg = hybrid_config(sz)
+        s_pre, b, ctx = sz["prefill"], sz["batch"], sz["ctx"]
+        bs = 32
+        mml = max(s_pre, ctx + 64)
+        nblocks = b * (-(-mml // bs)) + 1
+        res = {"metric": "hybrid_vs_dense_tokens_per_s", "size": name, "dtype": "bf16", "data": "synthetic (random weights)",
+               "roofline_peaks": {"hbm_gbs": hbm / 1e9, "bf16_tflops": peak / 1e12, "source": src},
+               "config": {"width": sz["width"], "layers": sz["layers"], "prefill_tokens": s_pre, "decode_batch": b,
+                          "decode_ctx": ctx, "l2": "flushed between timed steps"}}
+        # ---------------- hybrid
+        hm = HybridCausalLM(cfg, None, num_blocks=nblocks, max_num_seqs=b, max_model_len=mml, block_size=bs, device=dev)
+        per = -(-mml // bs)
+        rows = {r: list(range(1 + r * per, 1 + (r + 1) * per)) for r in range(b)}
+        for r, blk in rows.items():
+            hm.block_table[r, :per] = torch.tensor(blk, dtype=torch.int32, device=dev)
+        g = torch.Generator(device="cpu").manual_seed(0)
+        ptoks = torch.randint(0, sz["vocab"], (s_pre,), generator=g, dtype=torch.int32).to(dev)
+        pmeta = StepMeta.build([(0, 0, s_pre)], rows, bs, dev)
+        last = torch.tensor([s_pre - 1], device=dev)
+        dtoks = torch.randint(0, sz["vocab"], (b,), generator=g, dtype=torch.int32).to(dev)
+        dmeta = StepMeta.build([(r, ctx, 1) for r in range(b)], rows, bs, dev)
+        drows = torch.arange(b, device=dev)
+        h_pre = lambda: hm.forward(ptoks, pmeta, last)  # noqa: E731
+        h_dec = lambda: hm.forward(dtoks, dmeta, drows)  # noqa: E731
+        ms_p = _timed(h_pre, args.steps, args.warmup, flush)
+        ms_d = _timed(h_dec, args.steps, args.warmup, flush)
+        win = sz["attn"]["window"]
+        res["hybrid"] = {
+            "prefill_tok_s": round(s_pre / ms_p * 1e3), "prefill_ms": round(ms_p, 3),
+            "decode_tok_s": round(b / ms_d * 1e3), "decode_ms": round(ms_d, 3),
+            "prefill_kernels": _breakdown(h_pre, _floors(cfg, sz, s_pre, min(win, s_pre / 2), s_pre, 1), hbm, peak),
+            "decode_kernels": _breakdown(h_dec, _floors(cfg, sz, b, min(win, ctx + 1), b * min(win, ctx + 1), b), hbm, peak)}
+        del hm
+        torch.cuda.empty_cache()
+        # ---------------- dense decoder of equal size
+        shape = dense_shape(sz)
+        dm = B200CausalLM(shape, None, quant="bf16", num_blocks=nblocks, max_num_seqs=b, max_model_len=mml, block_size=bs, device=dev)
+        for r, blk in rows.items():
+            dm.block_table[r, :per] = torch.tensor(blk, dtype=torch.int32, device=dev)
+        ptok64 = ptoks.long()
+        d_pre = lambda: dm.prefill(0, ptok64, s_pre, 0)  # noqa: E731
+        bufs = dm.decode_buffers(b)
+        bufs.tokens.copy_(dtoks.long())
+
+        def d_dec():
+            dm.num_tokens[:b] = ctx + 1
+            dm.decode_step(b, max_ctx_blocks=-(-(ctx + 1) // bs))
+
+        ms_p2 = _timed(d_pre, args.steps, args.warmup, flush)
+        ms_d2 = _timed(d_dec, args.steps, args.warmup, flush)
+        hq, hkv, d = shape.num_q_heads, shape.num_kv_heads, shape.head_dim
+        dfl_p = {"paged_attn_prefill": (4.0 * hq * d * s_pre * (s_pre + 1) / 2, 4.0 * s_pre * hkv * d + 4.0 * s_pre * hq * d)}
+        dfl_d = {"paged_attn_decode": (4.0 * b * hq * d * (ctx + 1), 4.0 * b * (ctx + 1) * hkv * d)}
+        res["dense"] = {
+            "prefill_tok_s": round(s_pre / ms_p2 * 1e3), "prefill_ms": round(ms_p2, 3),
+            "decode_tok_s": round(b / ms_d2 * 1e3), "decode_ms": round(ms_d2, 3), "intermediate": shape.intermediate,
+            "prefill_kernels": _breakdown(d_pre, dfl_p, hbm, peak), "decode_kernels": _breakdown(d_dec, dfl_d, hbm, peak)}
+        del dm
+        torch.cuda.empty_cache()
+        res["gpu_launches"] = ops.launch_count()
+        print(json.dumps(res), flush=True)

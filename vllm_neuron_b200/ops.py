@@ -689,10 +689,10 @@ def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta,
 
 def ssd_scan(xbc, dt_src, dt_col0: int, a_log, dt_bias, d_skip, state, meta, heads: int, vdim: int, nstate: int, groups: int):
     """xbc [T, H*P + 2*G*N] (bf16 | fp32), raw dt = columns [dt_col0, dt_col0 + H) of the fp32 rows dt_src; state fp32
-    [slots, H, N, P] updated in place; returns y fp32 [T, H*P]."""
+    [slots, H, P, N] updated in place; returns y fp32 [T, H*P]."""
     _cuda(xbc, dt_src, state)
     _f32(dt_src, a_log, dt_bias, d_skip, state)
-    assert xbc.is_contiguous() and state.shape[1:] == (heads, nstate, vdim)
+    assert xbc.is_contiguous() and state.shape[1:] == (heads, vdim, nstate)
     t = xbc.shape[0]
     y = torch.empty((t, heads * vdim), dtype=torch.float32, device=xbc.device)
     with _k("ssd_scan"):
@@ -716,6 +716,9 @@ def kv_write_vmix(qkv, k_col0: int, v_col0: int, k_pool, v_pool, slot_mapping, *
                                               bs, _stream()), "b200_kv_write_vmix")
 
 
+PREFILL_ATTN_MIN_TOKENS = 16  # longest portion of a step from which the tensor-core attention kernel is used
+
+
 def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int):
     """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type."""
     _cuda(q_src, k_pool, v_pool, block_table, sink)
@@ -725,6 +728,17 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
     dv = v_pool.shape[3]
     t = q_src.shape[0]
     out = torch.empty((t, num_heads * dv), dtype=k_pool.dtype, device=q_src.device)
+    # prompt portions in bf16 serving: the tensor-core kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA per
+    # (token, head) on the CUDA cores
+    if (k_pool.dtype == torch.bfloat16 and meta.max_new >= PREFILL_ATTN_MIN_TOKENS and d % 16 == 0 and dv % 16 == 0
+            and d <= 512 and dv <= 256 and q_src.stride(0) % 2 == 0):
+        with _k("swa_sink_attn_prefill"):
+            check(_cabi.load().b200_swa_sink_attn_prefill(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                                          block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot),
+                                                          _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new, _ptr(sink), float(scale),
+                                                          int(window), _ptr(out), num_heads, g, d, dv, bs, _stream()),
+                  "b200_swa_sink_attn_prefill")
+        return out
     with _k("swa_sink_attn"):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
@@ -733,17 +747,15 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
     return out
 
 
-def moe_router(h, w_router, top: int):
-    """-> (expert ids int32 [T, top], routing weights fp32 [T, top] = sigmoid scores of the chosen experts)."""
-    _cuda(h, w_router)
-    assert h.dtype == w_router.dtype and h.is_contiguous() and w_router.is_contiguous()
-    t, width = h.shape
-    e = w_router.shape[0]
-    idx = torch.empty((t, top), dtype=torch.int32, device=h.device)
-    wt = torch.empty((t, top), dtype=torch.float32, device=h.device)
-    with _k("moe_router"):
-        check(_cabi.load().b200_moe_router(_ptr(h), _ptr(w_router), _edt(h), _ptr(idx), _ptr(wt), t, width, e, top, _stream()),
-              "b200_moe_router")
+def moe_topk(logits, top: int):
+    """fp32 router logits [T, E] -> (expert ids int32 [T, top], routing weights fp32 [T, top] = sigmoid of the chosen logits)."""
+    _cuda(logits)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    t, e = logits.shape
+    idx = torch.empty((t, top), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((t, top), dtype=torch.float32, device=logits.device)
+    with _k("moe_topk"):
+        check(_cabi.load().b200_moe_topk(_ptr(logits), logits.stride(0), _ptr(idx), _ptr(wt), t, e, top, _stream()), "b200_moe_topk")
     return idx, wt
 
 
