@@ -315,7 +315,7 @@ class HybridCausalLM:
                 lw.update(w_in=lin(p + "mix.in"), conv_w=vec(p + "mix.conv"), conv_b=vec(p + "mix.conv.b"),
                           dt_bias=vec(p + "mix.dt_bias"), a_log=vec(p + "mix.A_log"), d=vec(p + "mix.D"),
                           gnorm=vec(p + "mix.norm"), w_o=lin(p + "mix.o"),
-                          conv_state=torch.zeros((slots, m.conv - 1, m.channels), dtype=torch.float32, device=dev),
+                          conv_state=torch.zeros((slots, max(m.conv - 1, 1), m.channels), dtype=torch.float32, device=dev),
                           ssm_state=torch.zeros((slots, m.heads, m.vdim, m.state), dtype=torch.float32, device=dev))
             else:
                 lw.update(w_qkv=lin(p + "mix.q", p + "mix.k", p + "mix.v"), sink=vec(p + "mix.sink"), w_o=lin(p + "mix.o"),
@@ -324,7 +324,8 @@ class HybridCausalLM:
                 lw["vmix_mode"] = 0
                 if m.v_mix:
                     lw["vmix_mode"] = 1 if first_vmix else 2
-                    lw["lam"] = float(get(p + "mix.vmix").float())
+                    if not first_vmix:  # the first value-mixing layer's coefficient has no use
+                        lw["lam"] = float(get(p + "mix.vmix").float())
                     if first_vmix:
                         self._vfirst_cols = m.kv_heads * m.vdim
                     elif m.kv_heads * m.vdim != self._vfirst_cols:

@@ -677,7 +677,7 @@ def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta,
     _cuda(src, conv_w, conv_b, state)
     _f32(src, conv_w, conv_b, state)
     t, taps = src.shape[0], conv_w.shape[1]
-    assert conv_w.shape[0] == channels and state.shape[1:] == (taps - 1, channels)
+    assert conv_w.shape[0] == channels and state.shape[1:] == (max(taps - 1, 1), channels)  # one unused row when taps == 1
     out = torch.empty((t, channels), dtype=out_dtype, device=src.device)
     with _k("causal_conv_silu"):
         check(_cabi.load().b200_causal_conv_silu(_ptr(src), src.stride(0), col0, _ptr(conv_w), _ptr(conv_b), _ptr(state),
