@@ -313,10 +313,14 @@ int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w
                           void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
 /* Selective state-space scan: xbc [T][C] = [x: H*P | B: G*N | C: G*N] (x_dtype); dt_raw = dt_in[t][dt_col0 + h] (fp32);
  * dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(A_log[h]) dt) S + dt B x^T; y = S^T C + D[h] x.
- * state fp32 [slots][H][P][N], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256. */
+ * state fp32 [slots][H][P][N], updated; y fp32 [T][H*P].  Head h reads group h / (H / G).  N <= 256.
+ * segs (or NULL): int32 [num_segs][4] = {first token, end token, sequence, 1 (first of its sequence) | 2 (last)}, 16-byte
+ * aligned, a sequence's segments consecutive; seq_seg0 int32 [B + 1] = first segment of each sequence; scratch seg_state
+ * fp32 [num_segs][H][P][N] and seg_dtsum fp32 [num_segs][H].  Segments then run in parallel (three launches). */
 int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
                   const float* dt_bias, const float* D, float* state, const int32_t* seq_start, const int32_t* seq_slot,
-                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, void* stream);
+                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, const int32_t* segs, int num_segs,
+                  const int32_t* seq_seg0, float* seg_state, float* seg_dtsum, void* stream);
 /* Scatter keys [G][D] (columns k_col0..) and values [G][Dv] (columns v_col0..) of the fp32 rows `qkv` into the pools
  * K [num_blocks][G][block_size][D], V [num_blocks][G][block_size][Dv] by slot (slot < 0: skipped).
  * mode 0: plain; 1: also keep the unmixed values in v_first fp32 [T][G*Dv]; 2: cache v + lambda * (v_first - v) instead of v. */
@@ -339,19 +343,20 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
 /* Router decision over fp32 logits [T] rows of pitch ld: the `top` largest (ties to the lower index); weights = sigmoid of
  * the chosen logits (no renormalisation). */
 int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_weight, int T, int E, int top, void* stream);
-/* rows per expert tile of b200_moe_align / b200_grouped_linear */
+/* rows per expert tile of b200_moe_align / b200_grouped_linear; four times as many (tile_rows = 4 x this) are taken for
+ * prompt-sized batches of 16-byte aligned bf16 operands, where every weight tile then serves 128 rows */
 int b200_moe_tile_rows(void);
 /* Sort the npairs (token, choice) pairs by expert into tiles: sorted_ids [cap] (pair id or -1), tile_expert [max_tiles],
  * *num_tiles.  Needs max_tiles >= ceil(npairs / tile_rows) + E and cap >= max_tiles * tile_rows. */
 int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
-                   int32_t* num_tiles, void* stream);
+                   int32_t* num_tiles, int tile_rows, void* stream);
 /* out = A W_e^T, fp32 accumulation.  Dense (sorted_ids NULL): rows 0..M-1, one weight.  Grouped: row tile i belongs to
  * expert tile_expert[i]; row r of the tile list is pair sorted_ids[r]; its A row is pair / gather_div (gather_div > 0,
  * scaled by row_scale[pair]) or r itself; its out row is the pair id (scatter) or r.  glu: w_e = [gate; up] of N rows each
  * and out (dtype) = clamped GLU; else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit). */
 int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
                         int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
-                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, void* stream);
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, int tile_rows, void* stream);
 
 #ifdef __cplusplus
 }

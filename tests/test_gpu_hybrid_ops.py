@@ -74,7 +74,7 @@ def test_clamped_glu_limits():
     _close(ops.clamped_glu(gu.to(DEV), limit, torch.float32), gate * torch.sigmoid(1.702 * gate) * (up + 1), 2e-6)
 
 
-@pytest.mark.parametrize("taps", [2, 4, 5])
+@pytest.mark.parametrize("taps", [1, 2, 4, 5])
 def test_causal_conv_ragged_portions_and_slot_reuse(taps):
     """Three sequences advance by portions of 1, 2 and more tokens per step; a slot is then handed to a NEW sequence while it
     still holds the old one's inputs.  Every step's output must equal the whole-sequence convolution."""
@@ -84,7 +84,7 @@ def test_causal_conv_ragged_portions_and_slot_reuse(taps):
     g = torch.Generator().manual_seed(3)
     C, col0, ld = 45, 6, 60
     cw, cb = torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
-    state = torch.full((4, taps - 1, C), 7.0, device=DEV)     # garbage: a fresh sequence must not read it
+    state = torch.full((4, max(taps - 1, 1), C), 7.0, device=DEV)  # garbage: a fresh sequence must not read it (one unused row when taps == 1)
     seqs = {s: torch.randn(n, ld, generator=g) for s, n in ((0, 11), (1, 4), (2, 9), (3, 6))}
     want = {s: causal_conv_silu(u[:, col0:col0 + C].double(), cw.double(), cb.double()) for s, u in seqs.items()}
     slot = {0: 2, 1: 0, 2: 3, 3: 0}                           # sequence 3 reuses sequence 1's slot
@@ -101,15 +101,22 @@ def test_causal_conv_ragged_portions_and_slot_reuse(taps):
             done[s] += n
 
 
-@pytest.mark.parametrize("H,G,P,N", [(4, 2, 5, 12), (3, 3, 40, 40), (2, 1, 33, 70)])
-def test_selective_scan_ragged(H, G, P, N):
+SHORT_PLAN = ({0: 19, 1: 3, 2: 8}, [[(0, 7), (1, 1)], [(0, 1), (1, 2), (2, 2)], [(0, 11), (2, 6)]])
+# portions of 256 tokens and more are cut into parallel segments of 128: ragged last segments (44, 1 and 15 tokens), a
+# segmented portion that continues from a state left by an earlier segmented one, short sequences in the same step
+LONG_PLAN = ({0: 700, 1: 3, 2: 300}, [[(0, 300), (1, 1)], [(0, 1), (1, 2), (2, 257)], [(0, 399), (2, 43)]])
+
+
+@pytest.mark.parametrize("plan", [SHORT_PLAN, LONG_PLAN], ids=["short", "segmented"])
+@pytest.mark.parametrize("H,G,P,N", [(4, 2, 5, 12), (3, 3, 40, 40), (2, 1, 33, 70), (2, 2, 100, 64), (1, 1, 70, 130)])
+def test_selective_scan_ragged(H, G, P, N, plan):
     from oracle.pumopel_ref import selective_scan
 
     ops = _ops()
     g = torch.Generator().manual_seed(4)
     C = H * P + 2 * G * N
     a_log, dt_bias, d = torch.randn(H, generator=g) * 0.5, torch.randn(H, generator=g), torch.randn(H, generator=g)
-    lens = {0: 19, 1: 3, 2: 8}
+    lens, plan = plan
     xbc = {s: torch.randn(n, C, generator=g) for s, n in lens.items()}
     dts = {s: torch.randn(n, H + 3, generator=g) * 2 for s, n in lens.items()}   # dt = columns 3.. of wider rows
     want = {}
@@ -119,13 +126,14 @@ def test_selective_scan_ragged(H, G, P, N):
         Cm = xbc[s][:, H * P + G * N:].double().view(n, G, N).repeat_interleave(H // G, 1)
         want[s] = selective_scan(x, B, Cm, dts[s][:, 3:].double(), dt_bias.double(), a_log.double(), d.double()).reshape(n, H * P)
     state = torch.full((3, H, P, N), 5.0, device=DEV)
-    plan = [[(0, 7), (1, 1)], [(0, 1), (1, 2), (2, 2)], [(0, 11), (2, 6)]]
     done = {s: 0 for s in lens}
     for step in plan:
         entries = [(s, done[s], n) for s, n in step]
         xs = torch.cat([xbc[s][done[s]:done[s] + n] for s, n in step]).to(DEV)
         ds = torch.cat([dts[s][done[s]:done[s] + n] for s, n in step]).to(DEV)
-        y = ops.ssd_scan(xs, ds, 3, a_log.to(DEV), dt_bias.to(DEV), d.to(DEV), state, _meta(entries, {s: [1] * 16 for s, _ in step}), H, P, N, G)
+        meta = _meta(entries, {s: [1] * 128 for s, _ in step})
+        assert (meta.scan_segs is not None) == (max(n for _, n in step) >= 2 * ops.SCAN_SEGMENT)
+        y = ops.ssd_scan(xs, ds, 3, a_log.to(DEV), dt_bias.to(DEV), d.to(DEV), state, meta, H, P, N, G)
         o = 0
         for s, n in step:
             _close(y[o:o + n], want[s][done[s]:done[s] + n], 2e-5)
@@ -267,6 +275,35 @@ def test_moe_weight_on_the_input(E, top, shared):
     s = torch.sigmoid(h.double() @ W64["l0.mlp.router"].T)
     val, ref_idx = s.topk(top, dim=-1)
     assert torch.equal(idx.cpu().long(), ref_idx) and (wt.cpu().double() - val).abs().max() < 1e-6
+
+
+def test_moe_wide_tiles_match_the_default_tiles():
+    """Prompt-sized bf16 batch: experts with 128-row tiles (ragged tails, an expert that gets almost nothing) give the same
+    pairs as the 32-row tiles, and both follow the restatement evaluated on the bf16-rounded operands."""
+    from oracle.pumopel_ref import clamped_glu_expert
+
+    ops = _ops()
+    E, top, W, ff, T, limit = 5, 2, 64, 24, 700, 0.9
+    g = torch.Generator().manual_seed(21)
+    h = torch.randn(T, W, generator=g).bfloat16()
+    w_gu = (0.3 * torch.randn(E, 2 * ff, W, generator=g)).bfloat16()
+    w_dn = (0.3 * torch.randn(E, W, ff, generator=g)).bfloat16()
+    logits = torch.randn(T, E, generator=g)
+    logits[:, 3] -= 6.0                                     # expert 3 is chosen a handful of times at most
+    idx, wt = ops.moe_topk(logits.to(DEV), top)
+    hd, gud, dnd = h.to(DEV), w_gu.to(DEV), w_dn.to(DEV)
+    assert ops.moe_wide_tiles(hd, gud, T * top) == 4 * ops.moe_tile_rows()
+    assert ops.moe_wide_tiles(hd, gud, 10) is None and ops.moe_wide_tiles(hd.float(), gud.float(), T * top) is None
+    wide = ops.moe_experts(hd, wt, ops.moe_align(idx, E, 4 * ops.moe_tile_rows()), gud, dnd, top, limit)
+    base = ops.moe_experts(hd, wt, ops.moe_align(idx, E), gud, dnd, top, limit)
+    assert torch.equal(wide, base)                          # same K order per row: the tile height changes nothing
+    want = torch.zeros(T * top, W, dtype=torch.float64)
+    for pair in range(T * top):
+        e = int(idx.view(-1)[pair])
+        x = (h[pair // top].float() * wt.view(-1)[pair].cpu()).bfloat16().double()   # the weight goes into the operand
+        Wd = {"gate": w_gu[e, :ff].double(), "up": w_gu[e, ff:].double(), "down": w_dn[e].double()}
+        want[pair] = clamped_glu_expert(x[None], Wd, "", limit)[0]
+    _close(wide, want, 1e-2)                                # the activation between the two GEMMs is rounded to bf16
 
 
 def test_linear_paths_agree_with_matmul():

@@ -58,6 +58,21 @@ def test_step_meta_positions_and_slots():
     assert m.slot_mapping.dtype == torch.int64 and m.tok_pos.dtype == torch.int32
 
 
+def test_step_meta_cuts_long_portions_into_scan_segments():
+    from vllm_neuron_b200 import ops
+    from vllm_neuron_b200.hybrid import StepMeta
+
+    seg = ops.SCAN_SEGMENT
+    rows = {r: [1] * 64 for r in range(3)}
+    short = StepMeta.build([(0, 0, 2 * seg - 1), (1, 5, 1)], rows, 32, "cpu")
+    assert short.scan_segs is None and short.num_segs == 0
+    m = StepMeta.build([(0, 0, 2 * seg + 44), (1, 5, 1), (2, 7, 2 * seg)], rows, 32, "cpu")
+    a = 2 * seg + 44
+    assert m.scan_segs.tolist() == [[0, seg, 0, 1], [seg, 2 * seg, 0, 0], [2 * seg, a, 0, 2], [a, a + 1, 1, 3],
+                                    [a + 1, a + 1 + seg, 2, 1], [a + 1 + seg, a + 1 + 2 * seg, 2, 2]]
+    assert m.scan_seq_seg0.tolist() == [0, 3, 4, 6] and m.num_segs == 6
+
+
 def test_block_pool_reuses_freed_pages_and_never_hands_out_page_zero():
     p = BlockPool(6)
     a = p.allocate(3)

@@ -74,14 +74,14 @@ SIGNATURES = {
     "b200_gated_group_rmsnorm": (_i, [_p, _p, _i, _p, _p, _i, _i, _i, _i, _f, _p]),
     "b200_clamped_glu": (_i, [_p, _p, _i, _i, _i, _f, _p]),
     "b200_causal_conv_silu": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
-    "b200_ssd_scan": (_i, [_p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_ssd_scan": (_i, [_p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p]),
     "b200_kv_write_vmix": (_i, [_p, _i, _i, _i, _p, _f, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _p]),
     "b200_moe_topk": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_moe_tile_rows": (_i, []),
-    "b200_moe_align": (_i, [_p, _i, _i, _p, _i, _p, _i, _p, _p]),
-    "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _f, _p]),
+    "b200_moe_align": (_i, [_p, _i, _i, _p, _i, _p, _i, _p, _i, _p]),
+    "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _f, _i, _p]),
 }
 
 _lib = None

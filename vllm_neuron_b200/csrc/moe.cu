@@ -14,6 +14,7 @@
 namespace b200 {
 
 constexpr int MOE_BM = 32;
+constexpr int MOE_WIDE = 4;  // prompt-sized batches: tiles of MOE_BM * MOE_WIDE rows (tensor-core kernel only)
 constexpr int GL_BN = 64;
 constexpr int GL_BK = 16;
 constexpr int GL_THREADS = 256;
@@ -46,7 +47,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ z, int ld, int E, int 
 
 // single CTA: counts -> padded offsets -> tile owners -> scatter of pair ids
 __global__ void moe_align_kernel(const int32_t* __restrict__ idx, int npairs, int E, int32_t* __restrict__ sorted_ids, int cap,
-                                 int32_t* __restrict__ tile_expert, int max_tiles, int32_t* __restrict__ num_tiles) {
+                                 int32_t* __restrict__ tile_expert, int max_tiles, int32_t* __restrict__ num_tiles, int bm) {
   griddep_launch();
   griddep_wait();
   extern __shared__ int32_t sm[];
@@ -61,9 +62,9 @@ __global__ void moe_align_kernel(const int32_t* __restrict__ idx, int npairs, in
     int o = 0, nt = 0;
     for (int e = 0; e < E; ++e) {
       offs[e] = o;
-      const int tiles = (counts[e] + MOE_BM - 1) / MOE_BM;
+      const int tiles = (counts[e] + bm - 1) / bm;
       for (int k = 0; k < tiles && nt < max_tiles; ++k) tile_expert[nt++] = e;
-      o += tiles * MOE_BM;
+      o += tiles * bm;
     }
     *num_tiles = nt;
   }
@@ -181,7 +182,7 @@ constexpr int GM_BK = 32;
 constexpr int GM_LD = GM_BK + 8;
 constexpr int GM_WROWS = 128;
 
-template <int EPI>
+template <int EPI, int R>
 __global__ void __launch_bounds__(128)
     grouped_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
                        const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ w, int64_t w_stride,
@@ -189,11 +190,12 @@ __global__ void __launch_bounds__(128)
                        void* __restrict__ out, int ldo, int scatter, float limit) {
   griddep_launch();
   griddep_wait();
-  __shared__ __align__(16) __nv_bfloat16 As[MOE_BM][GM_LD];
+  constexpr int BM = MOE_BM * R;  // rows per tile: R sub-tiles of 32 share every weight tile
+  __shared__ __align__(16) __nv_bfloat16 As[BM][GM_LD];
   __shared__ __align__(16) __nv_bfloat16 Ws[GM_WROWS][GM_LD];
-  __shared__ int32_t rid[MOE_BM];
-  __shared__ int32_t oid[MOE_BM];
-  __shared__ float rsc[MOE_BM];
+  __shared__ int32_t rid[BM];
+  __shared__ int32_t oid[BM];
+  __shared__ float rsc[BM];
   const int tile = blockIdx.x;
   if (num_tiles && tile >= *num_tiles) return;
   const int e = tile_expert ? tile_expert[tile] : 0;
@@ -201,8 +203,8 @@ __global__ void __launch_bounds__(128)
   constexpr int BN = EPI == GL_EPI_GLU ? 64 : 128;  // outputs per CTA
   const int n0 = blockIdx.y * BN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid < MOE_BM) {
-    const int r = tile * MOE_BM + tid;
+  for (int i = tid; i < BM; i += 128) {
+    const int r = tile * BM + i;
     int src = -1, dst = -1;
     float sc = 1.0f;
     if (sorted_ids) {
@@ -215,15 +217,20 @@ __global__ void __launch_bounds__(128)
     } else if (r < M) {
       src = dst = r;
     }
-    rid[tid] = src;
-    oid[tid] = dst;
-    rsc[tid] = sc;
+    rid[i] = src;
+    oid[i] = dst;
+    rsc[i] = sc;
   }
   __syncthreads();
-  // global -> register staging: one 16-byte vector of A and four of W per thread and K step
+  // global -> register staging: R 16-byte vectors of A and four of W per thread and K step
   const int a_row = tid >> 2, kc = (tid & 3) * 8;
-  const int a_src = rid[a_row];
-  const float a_sc = rsc[a_row];
+  int a_src[R];
+  float a_sc[R];
+#pragma unroll
+  for (int rr = 0; rr < R; ++rr) {
+    a_src[rr] = rid[a_row + 32 * rr];
+    a_sc[rr] = rsc[a_row + 32 * rr];
+  }
   const __nv_bfloat16* w_ptr[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -238,18 +245,21 @@ __global__ void __launch_bounds__(128)
     }
     w_ptr[i] = n < N ? we + (int64_t)grow * K : nullptr;
   }
-  uint4 ra, rw[4];
+  uint4 ra[R], rw[4];
   auto fetch = [&](int k0) {
     const bool kin = k0 + kc < K;
-    ra = make_uint4(0, 0, 0, 0);
-    if (a_src >= 0 && kin) {
-      ra = *reinterpret_cast<const uint4*>(a + (int64_t)a_src * lda + k0 + kc);
-      if (a_sc != 1.0f) {
-        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ra);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h2[i]);
-          h2[i] = __floats2bfloat162_rn(f.x * a_sc, f.y * a_sc);
+    for (int rr = 0; rr < R; ++rr) {
+      ra[rr] = make_uint4(0, 0, 0, 0);
+      if (a_src[rr] >= 0 && kin) {
+        ra[rr] = *reinterpret_cast<const uint4*>(a + (int64_t)a_src[rr] * lda + k0 + kc);
+        if (a_sc[rr] != 1.0f) {
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ra[rr]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            h2[i] = __floats2bfloat162_rn(f.x * a_sc[rr], f.y * a_sc[rr]);
+          }
         }
       }
     }
@@ -257,9 +267,9 @@ __global__ void __launch_bounds__(128)
     for (int i = 0; i < 4; ++i)
       rw[i] = (w_ptr[i] && kin) ? *reinterpret_cast<const uint4*>(w_ptr[i] + k0 + kc) : make_uint4(0, 0, 0, 0);
   };
-  float acc[2][4][4];
+  float acc[2 * R][4][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 2 * R; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -268,32 +278,35 @@ __global__ void __launch_bounds__(128)
   auto nrow = [&](int j) { return EPI == GL_EPI_GLU ? (j < 2 ? 16 * warp + 8 * j : 64 + 16 * warp + 8 * (j - 2)) : 32 * warp + 8 * j; };
   fetch(0);
   for (int k0 = 0; k0 < K; k0 += GM_BK) {
-    *reinterpret_cast<uint4*>(&As[a_row][kc]) = ra;
+#pragma unroll
+    for (int rr = 0; rr < R; ++rr) *reinterpret_cast<uint4*>(&As[a_row + 32 * rr][kc]) = ra[rr];
 #pragma unroll
     for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(&Ws[(tid + 128 * i) >> 2][kc]) = rw[i];
     __syncthreads();
     if (k0 + GM_BK < K) fetch(k0 + GM_BK);
 #pragma unroll
     for (int kk = 0; kk < GM_BK; kk += 16) {
-      uint32_t af[2][4];
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) ldmatrix_x4(af[mt], smem_u32(&As[mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+      uint32_t bf[2][4];
 #pragma unroll
       for (int jp = 0; jp < 2; ++jp) {
-        uint32_t bf[4];
         const int mi = lane >> 3;  // matrix of the x4 load: tile 2 jp + mi / 2, k half mi % 2
-        ldmatrix_x4(bf, smem_u32(&Ws[nrow(2 * jp + (mi >> 1)) + (lane & 7)][kk + (mi & 1) * 8]));
+        ldmatrix_x4(bf[jp], smem_u32(&Ws[nrow(2 * jp + (mi >> 1)) + (lane & 7)][kk + (mi & 1) * 8]));
+      }
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          mma_bf16_16816(acc[mt][2 * jp], af[mt], bf[0], bf[1]);
-          mma_bf16_16816(acc[mt][2 * jp + 1], af[mt], bf[2], bf[3]);
+      for (int mt = 0; mt < 2 * R; ++mt) {
+        uint32_t af[4];
+        ldmatrix_x4(af, smem_u32(&As[mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+          mma_bf16_16816(acc[mt][2 * jp], af, bf[jp][0], bf[jp][1]);
+          mma_bf16_16816(acc[mt][2 * jp + 1], af, bf[jp][2], bf[jp][3]);
         }
       }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < 2 * R; ++mt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int r = mt * 16 + (lane >> 2) + (c >= 2 ? 8 : 0);
@@ -337,35 +350,44 @@ int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_we
 int b200_moe_tile_rows(void) { return MOE_BM; }
 
 int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
-                   int32_t* num_tiles, void* stream) {
+                   int32_t* num_tiles, int tile_rows, void* stream) {
   B200_REQUIRE(topk_idx && sorted_ids && tile_expert && num_tiles, "moe_align: null pointer");
   B200_REQUIRE(E >= 1 && E <= 4096, "moe_align: %d experts", E);
-  B200_REQUIRE(max_tiles >= (npairs + MOE_BM - 1) / MOE_BM + E && cap >= max_tiles * MOE_BM,
+  B200_REQUIRE(tile_rows == MOE_BM || tile_rows == MOE_BM * MOE_WIDE, "moe_align: %d rows per tile", tile_rows);
+  B200_REQUIRE(max_tiles >= (npairs + tile_rows - 1) / tile_rows + E && cap >= max_tiles * tile_rows,
                "moe_align: %d tiles / %d rows cannot hold %d pairs of %d experts", max_tiles, cap, npairs, E);
   if (npairs <= 0) return B200_OK;
   B200_CUDA_OK(launch_kernel(moe_align_kernel, dim3(1), dim3(1024), (size_t)2 * E * 4, (cudaStream_t)stream, topk_idx, npairs, E,
-                             sorted_ids, cap, tile_expert, max_tiles, num_tiles));
+                             sorted_ids, cap, tile_expert, max_tiles, num_tiles, tile_rows));
   return B200_OK;
 }
 
 int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
                         int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
-                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, void* stream) {
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, int tile_rows, void* stream) {
   B200_REQUIRE(a && w && out, "grouped_linear: null pointer");
   B200_REQUIRE(N > 0 && K > 0 && row_tiles >= 0, "grouped_linear: bad shape N=%d K=%d", N, K);
   B200_REQUIRE(sorted_ids || (!tile_expert && !num_tiles && !row_scale), "grouped_linear: expert tiles need the sorted pair list");
   if (row_tiles == 0) return B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == B200_BF16 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
+  const bool mma_ok = dtype == B200_BF16 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && !((uintptr_t)a & 15) &&
+                      !((uintptr_t)w & 15);
+  B200_REQUIRE(tile_rows == MOE_BM || (tile_rows == MOE_BM * MOE_WIDE && mma_ok),
+               "grouped_linear: %d rows per tile (32, or 128 for 16-byte aligned bf16 operands)", tile_rows);
+  if (mma_ok) {
     using BT = __nv_bfloat16;
-    if (glu)
-      B200_CUDA_OK(launch_kernel(grouped_mma_kernel<GL_EPI_GLU>, dim3(row_tiles, (N + 63) / 64), dim3(128), 0, st, (const BT*)a, lda,
-                                 sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N, K,
-                                 out, ldo, scatter, limit));
-    else
-      B200_CUDA_OK(launch_kernel(grouped_mma_kernel<GL_EPI_STORE>, dim3(row_tiles, (N + 127) / 128), dim3(128), 0, st, (const BT*)a,
-                                 lda, sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N,
-                                 K, out, ldo, scatter, limit));
+#define GM_LAUNCH(EPI, R, BN)                                                                                                \
+  B200_CUDA_OK(launch_kernel(grouped_mma_kernel<EPI, R>, dim3(row_tiles, (N + BN - 1) / BN), dim3(128), 0, st, (const BT*)a, lda, \
+                             sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N, K, \
+                             out, ldo, scatter, limit))
+    if (tile_rows == MOE_BM) {
+      if (glu) GM_LAUNCH(GL_EPI_GLU, 1, 64);
+      else GM_LAUNCH(GL_EPI_STORE, 1, 128);
+    } else {
+      if (glu) GM_LAUNCH(GL_EPI_GLU, MOE_WIDE, 64);
+      else GM_LAUNCH(GL_EPI_STORE, MOE_WIDE, 128);
+    }
+#undef GM_LAUNCH
     return B200_OK;
   }
   dim3 grid(row_tiles, (N + GL_BN - 1) / GL_BN);

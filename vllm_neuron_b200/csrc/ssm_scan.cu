@@ -73,53 +73,85 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
     if (k < taps - 1) st[(int64_t)k * C + c] = keep[k];
 }
 
-// Selective scan.  CTA = (32 value columns p of one head) x (8 slices of the state dimension); thread (p, s) keeps
-// S[p][n] for n = s, s + 8, ... (NPT of them) in registers across the tokens of its sequence; y is reduced over the 8
-// slices with shuffles.  The sequence is walked in chunks of SCAN_CHUNK tokens: the CTA stages the chunk's B, C and x rows
-// in shared memory with coalesced loads (fetched into registers one chunk ahead) and computes each token's step size and decay ONCE (softplus / exp are not
+// Selective scan.  CTA = (32 PP value columns p of one head) x (8 slices of the state dimension); thread (pl, s) keeps
+// S[p][n] for p = p0 + pl + 32 q (q < PP) and n = s, s + 8, ... (NPT of them) in registers across the tokens it walks, so
+// one B / C element read from shared memory serves PP columns; y is reduced over the 8 slices with shuffles.  Tokens are
+// walked in chunks of SCAN_CHUNK: the CTA stages the chunk's B, C and x rows in shared memory with coalesced loads
+// (fetched into registers one chunk ahead) and computes each token's step size and decay ONCE (softplus / exp are not
 // repeated by every thread), then the recurrence runs out of shared memory.  State layout [slots][H][P][N]: the 8 slices
 // of a column read consecutive floats.
-constexpr int SCAN_PCOLS = 32;
+//
+// Long prompt portions are cut into SEGMENTS of consecutive tokens that run in parallel (`segs` != NULL, blockIdx.z = segment):
+//   1. PARTIAL launch: every segment but a sequence's last starts from zero and leaves its end state S_loc and its summed
+//      step size in scratch (no y);
+//   2. ssd_seg_combine_kernel walks each sequence's segments once, elementwise: S_in[k+1] = exp(-exp(A_log) sum_dt[k]) S_in[k]
+//      + S_loc[k], S_in[0] = the slot's state (zero at position 0), and stores S_in[k] over the scratch;
+//   3. the full launch starts every segment from its S_in, writes y, and the last segment writes the slot's new state.
+// The recurrence is linear in S, so this is the sequential result up to fp32 rounding; everything stays fp32.
+constexpr int SCAN_PLANES = 32;
 constexpr int SCAN_SLICES = 8;
 constexpr int SCAN_CHUNK = 32;
+enum { SEG_FIRST = 1, SEG_LAST = 2 };
 
-template <typename XT, int NPT>
-__global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
+template <typename XT, int NPT, int PP, bool PARTIAL>
+__global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES)
     ssd_scan_kernel(const XT* __restrict__ xbc, int C, const float* __restrict__ dt_in, int ld_dt, int dt_col0,
                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
                     float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
-                    const int32_t* __restrict__ seq_pos0, float* __restrict__ y, int H, int P, int N, int G) {
+                    const int32_t* __restrict__ seq_pos0, float* __restrict__ y, int H, int P, int N, int G,
+                    const int4* __restrict__ segs, float* __restrict__ seg_state, float* __restrict__ seg_dtsum) {
   griddep_launch();
   griddep_wait();
   constexpr int NP = NPT * SCAN_SLICES;  // padded state size: rows of Bs / Cs
+  constexpr int PC = SCAN_PLANES * PP;   // value columns per CTA
   extern __shared__ float sm[];
   float* Bs = sm;                               // [SCAN_CHUNK][NP]
   float* Cs = Bs + SCAN_CHUNK * NP;             // [SCAN_CHUNK][NP]
-  float* xs = Cs + SCAN_CHUNK * NP;             // [SCAN_CHUNK][SCAN_PCOLS]
-  float* dts = xs + SCAN_CHUNK * SCAN_PCOLS;    // [SCAN_CHUNK]
+  float* xs = Cs + SCAN_CHUNK * NP;             // [SCAN_CHUNK][PC]
+  float* dts = xs + SCAN_CHUNK * PC;            // [SCAN_CHUNK]
   float* dec = dts + SCAN_CHUNK;                // [SCAN_CHUNK]
-  const int h = blockIdx.y, sq = blockIdx.z, tid = threadIdx.x;
+  const int h = blockIdx.y, tid = threadIdx.x;
+  int sq = blockIdx.z, t0, t1, flags = SEG_FIRST | SEG_LAST;
+  if (segs) {
+    const int4 sd = segs[blockIdx.z];
+    t0 = sd.x, t1 = sd.y, sq = sd.z, flags = sd.w;
+  } else {
+    t0 = seq_start[sq], t1 = seq_start[sq + 1];
+  }
+  if (PARTIAL && (flags & SEG_LAST)) return;  // nobody continues from a sequence's last segment in this step
   const int s = tid % SCAN_SLICES, pl = tid / SCAN_SLICES;
-  const int p0 = blockIdx.x * SCAN_PCOLS, p = p0 + pl;
-  const bool pv = p < P;
+  const int p0 = blockIdx.x * PC;
   const int g = h / (H / G);
   const int inner = H * P;
-  const int t0 = seq_start[sq], t1 = seq_start[sq + 1];
-  float* S0 = state + (((int64_t)seq_slot[sq] * H + h) * P + (pv ? p : 0)) * N;
-  float S[NPT];
-  const bool cont = seq_pos0[sq] > 0 && pv;
+  const int64_t head_elems = (int64_t)P * N;
+  // where this CTA's state comes from and goes to
+  const float* S_in = nullptr;
+  float* S_out = nullptr;
+  if (PARTIAL) {
+    S_out = seg_state + ((int64_t)(blockIdx.z + 1) * H + h) * head_elems;
+  } else {
+    float* slot = state + ((int64_t)seq_slot[sq] * H + h) * head_elems;
+    if (flags & SEG_FIRST) S_in = seq_pos0[sq] > 0 ? slot : nullptr;
+    else S_in = seg_state + ((int64_t)blockIdx.z * H + h) * head_elems;
+    if (flags & SEG_LAST) S_out = slot;
+  }
+  float S[PP][NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int n = s + i * SCAN_SLICES;
-    S[i] = (cont && n < N) ? S0[n] : 0.f;
+  for (int q = 0; q < PP; ++q) {
+    const int p = p0 + pl + SCAN_PLANES * q;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = s + i * SCAN_SLICES;
+      S[q][i] = (S_in && p < P && n < N) ? S_in[(int64_t)p * N + n] : 0.f;
+    }
   }
   const float negA = -expf(A_log[h]), bias = dt_bias[h], dsk = Dskip[h];
   const int64_t xcol = (int64_t)h * P + p0, bcol = (int64_t)inner + (int64_t)g * N, ccol = bcol + (int64_t)G * N;
   // global -> registers -> shared memory: the next chunk's loads are in flight while the current chunk is applied
-  constexpr int NTHR = SCAN_PCOLS * SCAN_SLICES;
+  constexpr int NTHR = SCAN_PLANES * SCAN_SLICES;
   constexpr int BC_PER = SCAN_CHUNK * NP / NTHR;
-  constexpr int X_PER = SCAN_CHUNK * SCAN_PCOLS / NTHR;
-  float rB[BC_PER], rC[BC_PER], rx[X_PER], rdt = 0.f;
+  constexpr int X_PER = SCAN_CHUNK * PC / NTHR;
+  float rB[BC_PER], rC[PARTIAL ? 1 : BC_PER], rx[X_PER], rdt = 0.f, dt_sum = 0.f;
   auto fetch = [&](int c0) {
     const int nc = t1 - c0 < SCAN_CHUNK ? t1 - c0 : SCAN_CHUNK;
 #pragma unroll
@@ -128,11 +160,11 @@ __global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
       const bool in = tok < nc && n < N;
       const XT* row = xbc + (int64_t)(c0 + (tok < nc ? tok : 0)) * C;
       rB[k] = in ? ldf(row, bcol + n) : 0.f;
-      rC[k] = in ? ldf(row, ccol + n) : 0.f;
+      if (!PARTIAL) rC[k] = in ? ldf(row, ccol + n) : 0.f;
     }
 #pragma unroll
     for (int k = 0; k < X_PER; ++k) {
-      const int i = tid + k * NTHR, tok = i / SCAN_PCOLS, pp = i - tok * SCAN_PCOLS;
+      const int i = tid + k * NTHR, tok = i / PC, pp = i - tok * PC;
       rx[k] = (tok < nc && p0 + pp < P) ? ldf(xbc + (int64_t)(c0 + tok) * C, xcol + pp) : 0.f;
     }
     if (tid < nc) rdt = dt_in[(int64_t)(c0 + tid) * ld_dt + dt_col0 + h];
@@ -144,7 +176,7 @@ __global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
 #pragma unroll
     for (int k = 0; k < BC_PER; ++k) {
       Bs[tid + k * NTHR] = rB[k];
-      Cs[tid + k * NTHR] = rC[k];
+      if (!PARTIAL) Cs[tid + k * NTHR] = rC[k];
     }
 #pragma unroll
     for (int k = 0; k < X_PER; ++k) xs[tid + k * NTHR] = rx[k];
@@ -153,49 +185,131 @@ __global__ void __launch_bounds__(SCAN_PCOLS* SCAN_SLICES)
       const float dt = z > 20.f ? z : log1pf(expf(z));  // softplus, no clamp on the step size
       dts[tid] = dt;
       dec[tid] = expf(negA * dt);
+      dt_sum += dt;
     }
     __syncthreads();
     if (c0 + SCAN_CHUNK < t1) fetch(c0 + SCAN_CHUNK);
     for (int tok = 0; tok < nc; ++tok) {
-      const float xc = xs[tok * SCAN_PCOLS + pl];
-      const float a = dec[tok], dx = dts[tok] * xc;
+      const float a = dec[tok], dtv = dts[tok];
+      float xc[PP], dx[PP], acc[PP];
+#pragma unroll
+      for (int q = 0; q < PP; ++q) {
+        xc[q] = xs[tok * PC + pl + SCAN_PLANES * q];
+        dx[q] = dtv * xc[q];
+        acc[q] = 0.f;
+      }
       const float* Br = Bs + tok * NP + s;
       const float* Cr = Cs + tok * NP + s;
-      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPT; i += 2) {
-        S[i] = a * S[i] + Br[i * SCAN_SLICES] * dx;
-        acc0 += S[i] * Cr[i * SCAN_SLICES];
-        S[i + 1] = a * S[i + 1] + Br[(i + 1) * SCAN_SLICES] * dx;
-        acc1 += S[i + 1] * Cr[(i + 1) * SCAN_SLICES];
+      for (int i = 0; i < NPT; ++i) {
+        const float bv = Br[i * SCAN_SLICES];
+        const float cv = PARTIAL ? 0.f : Cr[i * SCAN_SLICES];
+#pragma unroll
+        for (int q = 0; q < PP; ++q) {
+          S[q][i] = a * S[q][i] + bv * dx[q];
+          if (!PARTIAL) acc[q] += S[q][i] * cv;
+        }
       }
-      float acc = acc0 + acc1;
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (s == 0 && pv) y[(int64_t)(c0 + tok) * inner + xcol + pl] = acc + dsk * xc;
+      if (!PARTIAL) {
+#pragma unroll
+        for (int q = 0; q < PP; ++q) {
+          float v = acc[q];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          v += __shfl_xor_sync(0xffffffffu, v, 4);
+          const int pq = pl + SCAN_PLANES * q;
+          if (s == 0 && p0 + pq < P) y[(int64_t)(c0 + tok) * inner + xcol + pq] = v + dsk * xc[q];
+        }
+      }
     }
   }
-  if (pv) {
+  if (S_out) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int n = s + i * SCAN_SLICES;
-      if (n < N) S0[n] = S[i];
+    for (int q = 0; q < PP; ++q) {
+      const int p = p0 + pl + SCAN_PLANES * q;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const int n = s + i * SCAN_SLICES;
+        if (p < P && n < N) S_out[(int64_t)p * N + n] = S[q][i];
+      }
     }
+  }
+  if (PARTIAL && blockIdx.x == 0 && tid < 32) {  // the chunk's step sizes live in threads 0..31
+    const float tot = warp_sum(dt_sum);
+    if (tid == 0) seg_dtsum[(int64_t)blockIdx.z * H + h] = tot;
   }
 }
 
-template <typename XT, int NPT>
+// One thread per state element of a sequence: turns the segments' zero-start end states (scratch entry k + 1 holds segment
+// k's) into every segment's true start state, in place.
+__global__ void ssd_seg_combine_kernel(const float* __restrict__ state, float* __restrict__ seg_state,
+                                       const float* __restrict__ seg_dtsum, const float* __restrict__ A_log,
+                                       const int32_t* __restrict__ seq_seg0, const int32_t* __restrict__ seq_slot,
+                                       const int32_t* __restrict__ seq_pos0, int H, int64_t head_elems) {
+  griddep_launch();
+  griddep_wait();
+  const int sq = blockIdx.y;
+  const int v0 = seq_seg0[sq], nseg = seq_seg0[sq + 1] - v0;
+  if (nseg <= 1) return;
+  const int64_t per_seq = (int64_t)H * head_elems;
+  const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_seq) return;
+  const int h = (int)(e / head_elems);
+  const float negA = -expf(A_log[h]);
+  float S = seq_pos0[sq] > 0 ? state[(int64_t)seq_slot[sq] * per_seq + e] : 0.f;
+  for (int k = 1; k < nseg; ++k) {
+    const float d = expf(negA * seg_dtsum[(int64_t)(v0 + k - 1) * H + h]);
+    float* cell = seg_state + (int64_t)(v0 + k) * per_seq + e;
+    S = d * S + *cell;
+    *cell = S;
+  }
+}
+
+template <typename XT, int NPT, int PP>
 static int launch_scan(const void* xbc, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
                        const float* dt_bias, const float* Dskip, float* state, const int32_t* seq_start, const int32_t* seq_slot,
-                       const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, cudaStream_t stream) {
-  dim3 grid((P + SCAN_PCOLS - 1) / SCAN_PCOLS, H, B);
-  const size_t smem = (size_t)(SCAN_CHUNK * (2 * NPT * SCAN_SLICES + SCAN_PCOLS + 2)) * sizeof(float);
+                       const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, const int32_t* segs, int num_segs,
+                       const int32_t* seq_seg0, float* seg_state, float* seg_dtsum, cudaStream_t stream) {
+  constexpr int PC = SCAN_PLANES * PP;
+  dim3 grid((P + PC - 1) / PC, H, segs ? num_segs : B);
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * NPT * SCAN_SLICES + PC + 2)) * sizeof(float);
+  const int4* sd = reinterpret_cast<const int4*>(segs);
+  if (segs) {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(ssd_scan_kernel<XT, NPT, PP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT, PP, true>, grid, dim3(SCAN_PLANES * SCAN_SLICES), smem, stream,
+                               (const XT*)xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0,
+                               y, H, P, N, G, sd, seg_state, seg_dtsum));
+    const int64_t per_seq = (int64_t)H * P * N;
+    B200_CUDA_OK(launch_kernel(ssd_seg_combine_kernel, dim3((unsigned)((per_seq + 255) / 256), B), dim3(256), 0, stream,
+                               (const float*)state, seg_state, (const float*)seg_dtsum, A_log, seq_seg0, seq_slot, seq_pos0, H,
+                               (int64_t)P * N));
+  }
   if (smem > 48 * 1024)
-    B200_CUDA_OK(cudaFuncSetAttribute(ssd_scan_kernel<XT, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT>, grid, dim3(SCAN_PCOLS * SCAN_SLICES), smem, stream, (const XT*)xbc, C, dt_in,
-                             ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y, H, P, N, G));
+    B200_CUDA_OK(cudaFuncSetAttribute(ssd_scan_kernel<XT, NPT, PP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  B200_CUDA_OK(launch_kernel(ssd_scan_kernel<XT, NPT, PP, false>, grid, dim3(SCAN_PLANES * SCAN_SLICES), smem, stream,
+                             (const XT*)xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y,
+                             H, P, N, G, sd, seg_state, seg_dtsum));
   return B200_OK;
+}
+
+// columns per thread: as many as the head has 32-column planes, while the state stays within 64 registers
+template <typename XT, int NPT>
+static int pick_scan(const void* xbc, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log, const float* dt_bias,
+                     const float* Dskip, float* state, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
+                     float* y, int B, int H, int P, int N, int G, const int32_t* segs, int num_segs, const int32_t* seq_seg0,
+                     float* seg_state, float* seg_dtsum, cudaStream_t stream) {
+#define PICK_ARGS                                                                                                             \
+  xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y, B, H, P, N, G, segs, num_segs, \
+      seq_seg0, seg_state, seg_dtsum, stream
+  if constexpr (NPT * 4 <= 64) {
+    if (P > 64) return launch_scan<XT, NPT, 4>(PICK_ARGS);
+  }
+  if constexpr (NPT * 2 <= 64) {
+    if (P > 32) return launch_scan<XT, NPT, 2>(PICK_ARGS);
+  }
+  return launch_scan<XT, NPT, 1>(PICK_ARGS);
+#undef PICK_ARGS
 }
 
 }  // namespace b200
@@ -223,19 +337,24 @@ int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w
 
 int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log,
                   const float* dt_bias, const float* D, float* state, const int32_t* seq_start, const int32_t* seq_slot,
-                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, void* stream) {
+                  const int32_t* seq_pos0, float* y, int B, int H, int P, int N, int G, const int32_t* segs, int num_segs,
+                  const int32_t* seq_seg0, float* seg_state, float* seg_dtsum, void* stream) {
   B200_REQUIRE(xbc && dt_in && A_log && dt_bias && D && state && seq_start && seq_slot && seq_pos0 && y, "ssd_scan: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "ssd_scan: %d heads do not split into %d groups", H, G);
   B200_REQUIRE(N >= 1 && N <= 256, "ssd_scan: state size %d (1..256 supported)", N);
   B200_REQUIRE(C == H * P + 2 * G * N, "ssd_scan: %d channels != heads * vdim + 2 * groups * state", C);
+  B200_REQUIRE(!segs || (num_segs >= B && seq_seg0 && seg_state && seg_dtsum && !((uintptr_t)segs & 15)),
+               "ssd_scan: the segment list needs its per-sequence offsets and scratch");
   if (B <= 0) return B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
-#define SCAN_ARGS xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, D, state, seq_start, seq_slot, seq_pos0, y, B, H, P, N, G, st
+#define SCAN_ARGS                                                                                                          \
+  xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, D, state, seq_start, seq_slot, seq_pos0, y, B, H, P, N, G, segs, num_segs, \
+      seq_seg0, seg_state, seg_dtsum, st
   B200_DISPATCH_ELEM(x_dtype, XT, {
-    if (N <= 32) return launch_scan<XT, 4>(SCAN_ARGS);
-    if (N <= 64) return launch_scan<XT, 8>(SCAN_ARGS);
-    if (N <= 128) return launch_scan<XT, 16>(SCAN_ARGS);
-    return launch_scan<XT, 32>(SCAN_ARGS);
+    if (N <= 32) return pick_scan<XT, 4>(SCAN_ARGS);
+    if (N <= 64) return pick_scan<XT, 8>(SCAN_ARGS);
+    if (N <= 128) return pick_scan<XT, 16>(SCAN_ARGS);
+    return pick_scan<XT, 32>(SCAN_ARGS);
   });
 #undef SCAN_ARGS
   return B200_OK;

@@ -230,6 +230,12 @@ class StepMeta:
     tok_pos: torch.Tensor
     slot_mapping: torch.Tensor  # int64 [T]: KV slot = block id * block_size + offset
     max_new: int = 0            # longest portion of the step (host)
+    # long portions cut into segments the selective scan runs in parallel: int32 [num_segs, 4] = (first token, end token,
+    # sequence, 1 = first of its sequence | 2 = last) and int32 [num_seqs + 1] first segment per sequence; None when no
+    # portion of the step is long enough
+    scan_segs: torch.Tensor | None = None
+    scan_seq_seg0: torch.Tensor | None = None
+    num_segs: int = 0
 
     @staticmethod
     def build(entries, block_rows, block_size: int, device) -> "StepMeta":
@@ -263,7 +269,24 @@ class StepMeta:
         for a in parts:
             cut.append(dev[o:o + a.size])
             o += a.size
-        return StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64), int(n.max()) if b else 0)
+        meta = StepMeta(b, t, *cut, dev[i32.size:i32.size + 2 * t].view(torch.int64), int(n.max()) if b else 0)
+        seg = ops.SCAN_SEGMENT
+        if meta.max_new >= 2 * seg:
+            per = np.maximum(1, -(-n // seg))
+            seg0 = np.zeros(b + 1, dtype=np.int64)
+            np.cumsum(per, out=seg0[1:])
+            v = int(seg0[-1])
+            sq = np.repeat(np.arange(b, dtype=np.int64), per)
+            k = np.arange(v, dtype=np.int64) - seg0[sq]
+            first = start[sq] + k * seg
+            end = np.minimum(first + seg, start[sq + 1])
+            flags = (k == 0) * 1 + (k == per[sq] - 1) * 2
+            hs = torch.from_numpy(np.concatenate([np.stack([first, end, sq, flags], axis=1).reshape(-1), seg0]).astype(np.int32))
+            if torch.device(device).type == "cuda":
+                hs = hs.pin_memory()
+            ds = hs.to(device, non_blocking=True)
+            meta.scan_segs, meta.scan_seq_seg0, meta.num_segs = ds[:4 * v].view(v, 4), ds[4 * v:], v
+        return meta
 
 
 # ------------------------------------------------------------------------------------------------ the model
@@ -396,7 +419,8 @@ class HybridCausalLM:
     def _moe(self, lw, h):
         f = lw["spec"].mlp
         idx, wt = ops.moe_topk(self._linear(h, lw["w_router"]), f.top)  # fp32 logits, sigmoid scores
-        pairs = ops.moe_experts(h, wt, ops.moe_align(idx, f.experts), lw["w_gu"], lw["w_down"], f.top, f.limit)
+        align = ops.moe_align(idx, f.experts, ops.moe_wide_tiles(h, lw["w_gu"], idx.numel()))
+        pairs = ops.moe_experts(h, wt, align, lw["w_gu"], lw["w_down"], f.top, f.limit)
         shared = None
         if f.shared_ff:
             shared = self._linear(ops.clamped_glu(self._linear(h, lw["sh_gu"]), f.shared_limit, self.et), lw["sh_down"])

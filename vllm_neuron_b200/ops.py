@@ -687,19 +687,30 @@ def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta,
     return out
 
 
+SCAN_SEGMENT = 128  # tokens per parallel segment of a long portion in the selective scan
+
+
 def ssd_scan(xbc, dt_src, dt_col0: int, a_log, dt_bias, d_skip, state, meta, heads: int, vdim: int, nstate: int, groups: int):
     """xbc [T, H*P + 2*G*N] (bf16 | fp32), raw dt = columns [dt_col0, dt_col0 + H) of the fp32 rows dt_src; state fp32
-    [slots, H, P, N] updated in place; returns y fp32 [T, H*P]."""
+    [slots, H, P, N] updated in place; returns y fp32 [T, H*P].  When the step carries a segment list (meta.scan_segs: some
+    portion is long) the segments run in parallel from scratch states that a combine pass chains together."""
     _cuda(xbc, dt_src, state)
     _f32(dt_src, a_log, dt_bias, d_skip, state)
     assert xbc.is_contiguous() and state.shape[1:] == (heads, vdim, nstate)
     t = xbc.shape[0]
     y = torch.empty((t, heads * vdim), dtype=torch.float32, device=xbc.device)
+    segs = getattr(meta, "scan_segs", None)
+    nseg = meta.num_segs if segs is not None else 0
+    seg_state = seg_dt = None
+    if nseg:
+        seg_state = torch.empty((nseg + 1, heads, vdim, nstate), dtype=torch.float32, device=xbc.device)
+        seg_dt = torch.empty((nseg, heads), dtype=torch.float32, device=xbc.device)
     with _k("ssd_scan"):
         check(_cabi.load().b200_ssd_scan(_ptr(xbc), _edt(xbc), xbc.shape[1], _ptr(dt_src), dt_src.stride(0), dt_col0, _ptr(a_log),
                                          _ptr(dt_bias), _ptr(d_skip), _ptr(state), _ptr(meta.seq_start), _ptr(meta.seq_slot),
-                                         _ptr(meta.seq_pos0), _ptr(y), meta.num_seqs, heads, vdim, nstate, groups, _stream()),
-              "b200_ssd_scan")
+                                         _ptr(meta.seq_pos0), _ptr(y), meta.num_seqs, heads, vdim, nstate, groups,
+                                         _ptr(segs) if nseg else 0, nseg, _ptr(meta.scan_seq_seg0) if nseg else 0,
+                                         _ptr(seg_state), _ptr(seg_dt), _stream()), "b200_ssd_scan")
     return y
 
 
@@ -763,11 +774,12 @@ def moe_tile_rows() -> int:
     return int(_cabi.load().b200_moe_tile_rows())
 
 
-def moe_align(topk_idx, num_experts: int):
-    """-> (sorted pair ids int32 [cap] padded with -1, tile owners int32 [max_tiles], device count of used tiles [1])."""
+def moe_align(topk_idx, num_experts: int, tile_rows: int | None = None):
+    """-> (sorted pair ids int32 [cap] padded with -1, tile owners int32 [max_tiles], device count of used tiles [1], rows per
+    tile).  tile_rows: moe_tile_rows() (default) or four times that for prompt-sized bf16 batches."""
     _cuda(topk_idx)
     assert topk_idx.dtype == torch.int32 and topk_idx.is_contiguous()
-    n, bm = topk_idx.numel(), moe_tile_rows()
+    n, bm = topk_idx.numel(), tile_rows or moe_tile_rows()
     max_tiles = -(-n // bm) + num_experts
     dev = topk_idx.device
     sorted_ids = torch.empty(max_tiles * bm, dtype=torch.int32, device=dev)
@@ -775,8 +787,17 @@ def moe_align(topk_idx, num_experts: int):
     num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
     with _k("moe_align"):
         check(_cabi.load().b200_moe_align(_ptr(topk_idx), n, num_experts, _ptr(sorted_ids), sorted_ids.numel(), _ptr(tile_expert),
-                                          max_tiles, _ptr(num_tiles), _stream()), "b200_moe_align")
-    return sorted_ids, tile_expert, num_tiles
+                                          max_tiles, _ptr(num_tiles), bm, _stream()), "b200_moe_align")
+    return sorted_ids, tile_expert, num_tiles, bm
+
+
+def moe_wide_tiles(h, w_gate_up, num_pairs: int) -> int | None:
+    """Rows per expert tile for this batch: the wide tile once the experts see about 64 rows each on average and the
+    operands suit the tensor-core kernel, else None (the default tile)."""
+    e, ff2, width = w_gate_up.shape
+    if h.dtype == torch.bfloat16 and width % 8 == 0 and (ff2 // 2) % 8 == 0 and h.stride(0) % 8 == 0 and num_pairs >= 64 * e:
+        return 4 * moe_tile_rows()
+    return None
 
 
 def linear_simt(a, w):
@@ -789,7 +810,7 @@ def linear_simt(a, w):
     out = torch.empty((m, n), dtype=torch.float32, device=a.device)
     with _k(f"linear_simt[{m}x{n}x{k}]"):
         check(_cabi.load().b200_grouped_linear(_ptr(a), a.stride(0), 0, 0, 0, _ptr(w), 0, 0, 0, -(-m // moe_tile_rows()), m, n, k,
-                                               _edt(a), _ptr(out), n, 0, 0, 0.0, _stream()), "b200_grouped_linear")
+                                               _edt(a), _ptr(out), n, 0, 0, 0.0, moe_tile_rows(), _stream()), "b200_grouped_linear")
     return out
 
 
@@ -797,7 +818,7 @@ def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float
     """Routed experts: for every (token, choice) pair  W_down glu(W_gate_up (weight * h)).  h [T, W]; w_gate_up
     [E, 2 ff, W] (gate rows first), w_down [E, W, ff]; returns fp32 [T * top, W] in pair order."""
     _cuda(h, topk_weight, w_gate_up, w_down)
-    sorted_ids, tile_expert, num_tiles = align
+    sorted_ids, tile_expert, num_tiles, bm = align
     e, ff2, width = w_gate_up.shape
     ff = ff2 // 2
     tiles = tile_expert.numel()
@@ -807,9 +828,9 @@ def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float
     with _k("moe_gate_up_glu"):
         check(lib.b200_grouped_linear(_ptr(h), h.stride(0), _ptr(sorted_ids), top, _ptr(topk_weight), _ptr(w_gate_up), ff2 * width,
                                       _ptr(tile_expert), _ptr(num_tiles), tiles, 0, ff, width, _edt(h), _ptr(act), ff, 0, 1,
-                                      float(limit), _stream()), "b200_grouped_linear")
+                                      float(limit), bm, _stream()), "b200_grouped_linear")
     with _k("moe_down"):
         check(lib.b200_grouped_linear(_ptr(act), ff, _ptr(sorted_ids), 0, 0, _ptr(w_down), width * ff, _ptr(tile_expert),
-                                      _ptr(num_tiles), tiles, 0, width, ff, _edt(h), _ptr(out), width, 1, 0, 0.0, _stream()),
+                                      _ptr(num_tiles), tiles, 0, width, ff, _edt(h), _ptr(out), width, 1, 0, 0.0, bm, _stream()),
               "b200_grouped_linear")
     return out
