@@ -3,7 +3,7 @@
 //   * kv_write_vmix: scatters this step's keys and values into the pools by slot; optionally mixes the value with the
 //     value the first value-mixing layer produced for the same token, v + lambda (v_first - v), BEFORE it is
 //     cached (what is cached is what every later query reads);
-//   * swa_sink_attn: ragged batch, one CTA per (token, query head).  A query at position i attends keys i - window < j <= i,
+//   * swa_sink_attn: ragged batch, one CTA per (token, up to 4 query heads of one kv head).  A query at position i attends keys i - window < j <= i,
 //     read through the sequence's block table.  Online softmax in fp32 that STARTS from the sink: running maximum =
 //     sink logit, running denominator = 1, accumulator = 0 -- the sink adds exp(sink) to the denominator once, has no key,
 //     no value, and is not multiplied by the score scale.
@@ -40,40 +40,68 @@ __global__ void kv_write_vmix_kernel(const float* __restrict__ qkv, int ld, int 
 
 constexpr int ATT_WARPS = 4;
 
-// q (fp32, shared memory) . k row, with 16-byte loads when the row allows it
-template <typename KT>
-__device__ __forceinline__ float dot_q_row(const float* __restrict__ qs, const KT* __restrict__ kr, int D);
-template <>
-__device__ __forceinline__ float dot_q_row<float>(const float* __restrict__ qs, const float* __restrict__ kr, int D) {
-  float dot = 0.f;
+// QH query rows (fp32, shared memory, pitch D) . one k row, with 16-byte loads when the row allows it: the key row is
+// fetched once for all the query heads of its group that the CTA serves
+template <int QH>
+__device__ __forceinline__ void dot_q_rows_f32(const float* __restrict__ qs, int Dp, const float* __restrict__ kr, int D,
+                                               float (&dot)[QH]) {
   if ((D & 3) == 0) {
+#pragma unroll 4
     for (int d = 0; d < D; d += 4) {
       const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
-      dot += qs[d] * k4.x + qs[d + 1] * k4.y + qs[d + 2] * k4.z + qs[d + 3] * k4.w;
-    }
-  } else {
-    for (int d = 0; d < D; ++d) dot += qs[d] * kr[d];
-  }
-  return dot;
-}
-template <>
-__device__ __forceinline__ float dot_q_row<__nv_bfloat16>(const float* __restrict__ qs, const __nv_bfloat16* __restrict__ kr, int D) {
-  float dot = 0.f;
-  if ((D & 7) == 0) {
-    for (int d = 0; d < D; d += 8) {
-      const uint4 k8 = *reinterpret_cast<const uint4*>(kr + d);
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&k8);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h2[i]);
-        dot += qs[d + 2 * i] * f.x + qs[d + 2 * i + 1] * f.y;
+      for (int q = 0; q < QH; ++q) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + q * Dp + d);
+        dot[q] += q4.x * k4.x + q4.y * k4.y + q4.z * k4.z + q4.w * k4.w;
       }
     }
   } else {
-    for (int d = 0; d < D; ++d) dot += qs[d] * __bfloat162float(kr[d]);
+    for (int d = 0; d < D; ++d) {
+      const float kv = kr[d];
+#pragma unroll
+      for (int q = 0; q < QH; ++q) dot[q] += qs[q * Dp + d] * kv;
+    }
   }
-  return dot;
 }
+template <int QH>
+__device__ __forceinline__ void dot_q_rows_bf16(const float* __restrict__ qs, int Dp, const __nv_bfloat16* __restrict__ kr, int D,
+                                                float (&dot)[QH]) {
+  if ((D & 7) == 0) {
+#pragma unroll 4
+    for (int d = 0; d < D; d += 8) {
+      const uint4 k8 = *reinterpret_cast<const uint4*>(kr + d);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&k8);
+      const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]), f2 = __bfloat1622float2(h2[2]),
+                   f3 = __bfloat1622float2(h2[3]);
+#pragma unroll
+      for (int q = 0; q < QH; ++q) {
+        const float4 qa = *reinterpret_cast<const float4*>(qs + q * Dp + d);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + q * Dp + d + 4);
+        dot[q] += qa.x * f0.x + qa.y * f0.y + qa.z * f1.x + qa.w * f1.y + qb.x * f2.x + qb.y * f2.y + qb.z * f3.x + qb.w * f3.y;
+      }
+    }
+  } else {
+    for (int d = 0; d < D; ++d) {
+      const float kv = __bfloat162float(kr[d]);
+#pragma unroll
+      for (int q = 0; q < QH; ++q) dot[q] += qs[q * Dp + d] * kv;
+    }
+  }
+}
+template <typename KT, int QH>
+struct DotRows;
+template <int QH>
+struct DotRows<float, QH> {
+  static __device__ __forceinline__ void run(const float* qs, int Dp, const float* kr, int D, float (&dot)[QH]) {
+    dot_q_rows_f32<QH>(qs, Dp, kr, D, dot);
+  }
+};
+template <int QH>
+struct DotRows<__nv_bfloat16, QH> {
+  static __device__ __forceinline__ void run(const float* qs, int Dp, const __nv_bfloat16* kr, int D, float (&dot)[QH]) {
+    dot_q_rows_bf16<QH>(qs, Dp, kr, D, dot);
+  }
+};
 // two consecutive elements of a value row (pairs: lane l owns columns 2 l, 2 l + 1 of every 64-column slab)
 __device__ __forceinline__ float2 ld_pair(const float* r, int d, int Dv, bool vec) {
   if (vec) return *reinterpret_cast<const float2*>(r + d);
@@ -84,11 +112,12 @@ __device__ __forceinline__ float2 ld_pair(const __nv_bfloat16* r, int d, int Dv,
   return make_float2(d < Dv ? __bfloat162float(r[d]) : 0.f, d + 1 < Dv ? __bfloat162float(r[d + 1]) : 0.f);
 }
 
-// One CTA per (token, query head): its 4 warps take the window's 32-key tiles round-robin (lane-per-key scores,
-// lanes-over-columns value accumulation, each warp its own running maximum / denominator / accumulator) and merge through
-// shared memory.  Warp 0 carries the sink's 1 in the denominator.  The split depends on the position and the window only.
+// One CTA per (token, QH query heads that share a kv head): its 4 warps take the window's 32-key tiles round-robin
+// (lane-per-key scores, lanes-over-columns value accumulation, each warp its own running maximum / denominator /
+// accumulator per head) and merge through shared memory.  Every K and V row is fetched once for the QH heads.  Warp 0
+// carries the sink's 1 in the denominators.  The split depends on the position and the window only.
 // Serves decoded tokens and short portions in both element types, and every shape in 32-bit serving.
-template <typename KT, int MAXC>
+template <typename KT, int MAXC, int QH>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
     swa_sink_attn_kernel(const float* __restrict__ q, int ldq, const KT* __restrict__ k_pool, const KT* __restrict__ v_pool,
                          const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
@@ -96,86 +125,110 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                          KT* __restrict__ out, int T, int H, int G, int D, int Dv, int bs) {
   griddep_launch();
   griddep_wait();
-  extern __shared__ float sm_att[];
-  float* qs = sm_att;                      // [D]
-  float* accs = qs + D;                    // [ATT_WARPS][64 MAXC]
-  float* ml = accs + ATT_WARPS * 64 * MAXC;  // [ATT_WARPS][2]
+  extern __shared__ __align__(16) float sm_att[];
+  const int Dp = (D + 3) & ~3;                    // pitch of a query row: 16-byte aligned rows
+  float* qs = sm_att;                             // [QH][Dp]
+  float* accs = qs + QH * Dp;                     // [ATT_WARPS][QH][64 MAXC]
+  float* ml = accs + ATT_WARPS * QH * 64 * MAXC;  // [ATT_WARPS][QH][2]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x / H, h = blockIdx.x - t * H;
-  const int g = h / (H / G);
-  for (int d = threadIdx.x; d < D; d += ATT_WARPS * 32) qs[d] = q[(int64_t)t * ldq + (int64_t)h * D + d];
+  const int hb = H / QH;                          // head blocks per token
+  const int t = blockIdx.x / hb, h0 = (blockIdx.x - t * hb) * QH;
+  const int g = h0 / (H / G);                     // QH divides H / G: the block's heads share this kv head
+  for (int i = threadIdx.x; i < QH * D; i += ATT_WARPS * 32) {
+    const int qh = i / D, d = i - qh * D;
+    qs[qh * Dp + d] = q[(int64_t)t * ldq + (int64_t)(h0 + qh) * D + d];
+  }
   __syncthreads();
   const int pos = tok_pos[t];
   const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
   const int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
   const bool vvec = (Dv & 1) == 0;
-  float m = sink[h], l = warp == 0 ? 1.0f : 0.f;  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
-  float2 acc[MAXC];
+  float m[QH], l[QH];  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
+  float2 acc[QH][MAXC];
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c) acc[c] = make_float2(0.f, 0.f);
+  for (int qh = 0; qh < QH; ++qh) {
+    m[qh] = sink[h0 + qh];
+    l[qh] = warp == 0 ? 1.0f : 0.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) acc[qh][c] = make_float2(0.f, 0.f);
+  }
   for (int j0 = lo + 32 * warp; j0 <= pos; j0 += 32 * ATT_WARPS) {
     const int j = j0 + lane;
     const bool valid = j <= pos;
     int64_t tile = 0;  // row index of (block, kv head, token) in the pools
-    float s = -INFINITY;
+    float p[QH];
+#pragma unroll
+    for (int qh = 0; qh < QH; ++qh) p[qh] = 0.f;
     if (valid) {
       const int64_t blk = bt[j / bs];
       tile = (blk * G + g) * bs + (j % bs);
-      s = dot_q_row(qs, k_pool + tile * D, D) * scale;
+      DotRows<KT, QH>::run(qs, Dp, k_pool + tile * D, D, p);
     }
-    const float m_new = fmaxf(m, warp_max(s));
-    const float corr = expf(m - m_new);
-    const float p = valid ? expf(s - m_new) : 0.f;
-    l = l * corr + warp_sum(p);
 #pragma unroll
-    for (int c = 0; c < MAXC; ++c) {
-      acc[c].x *= corr;
-      acc[c].y *= corr;
+    for (int qh = 0; qh < QH; ++qh) {
+      const float s = valid ? p[qh] * scale : -INFINITY;
+      const float m_new = fmaxf(m[qh], warp_max(s));
+      const float corr = expf(m[qh] - m_new);
+      p[qh] = valid ? expf(s - m_new) : 0.f;
+      l[qh] = l[qh] * corr + warp_sum(p[qh]);
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c) {
+        acc[qh][c].x *= corr;
+        acc[qh][c].y *= corr;
+      }
+      m[qh] = m_new;
     }
-    m = m_new;
-    const int cnt = pos - j0 + 1 < 32 ? pos - j0 + 1 : 32;
-    for (int jj = 0; jj < cnt; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
+    // all 32 keys of the tile, eight value rows in flight: lanes past the last key hold p = 0 and row 0 of the pools (the
+    // null page: finite values), so they add nothing
+#pragma unroll 8
+    for (int jj = 0; jj < 32; ++jj) {
       const int64_t tj = __shfl_sync(0xffffffffu, tile, jj);
+      float pj[QH];
+#pragma unroll
+      for (int qh = 0; qh < QH; ++qh) pj[qh] = __shfl_sync(0xffffffffu, p[qh], jj);
       const KT* vr = v_pool + tj * Dv;
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
         const int d = 2 * lane + 64 * c;
         if (d < Dv) {
           const float2 v2 = ld_pair(vr, d, Dv, vvec);
-          acc[c].x += pj * v2.x;
-          acc[c].y += pj * v2.y;
+#pragma unroll
+          for (int qh = 0; qh < QH; ++qh) {
+            acc[qh][c].x += pj[qh] * v2.x;
+            acc[qh][c].y += pj[qh] * v2.y;
+          }
         }
       }
     }
   }
   // ---- merge the warps (fixed order 0..3)
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c) {
-    accs[(warp * MAXC + c) * 64 + 2 * lane] = acc[c].x;
-    accs[(warp * MAXC + c) * 64 + 2 * lane + 1] = acc[c].y;
-  }
-  if (lane == 0) {
-    ml[2 * warp] = m;
-    ml[2 * warp + 1] = l;
+  for (int qh = 0; qh < QH; ++qh) {
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      accs[((warp * QH + qh) * MAXC + c) * 64 + 2 * lane] = acc[qh][c].x;
+      accs[((warp * QH + qh) * MAXC + c) * 64 + 2 * lane + 1] = acc[qh][c].y;
+    }
+    if (lane == 0) {
+      ml[2 * (warp * QH + qh)] = m[qh];
+      ml[2 * (warp * QH + qh) + 1] = l[qh];
+    }
   }
   __syncthreads();
-  float mt = ml[0];
+  for (int i = threadIdx.x; i < QH * Dv; i += ATT_WARPS * 32) {
+    const int qh = i / Dv, d = i - qh * Dv;
+    float mt = ml[2 * qh];
 #pragma unroll
-  for (int w = 1; w < ATT_WARPS; ++w) mt = fmaxf(mt, ml[2 * w]);
-  float lt = 0.f, f[ATT_WARPS];
-#pragma unroll
-  for (int w = 0; w < ATT_WARPS; ++w) {
-    f[w] = expf(ml[2 * w] - mt);
-    lt += ml[2 * w + 1] * f[w];
-  }
-  const float inv = 1.0f / lt;
-  for (int d = threadIdx.x; d < Dv; d += ATT_WARPS * 32) {
+    for (int w = 1; w < ATT_WARPS; ++w) mt = fmaxf(mt, ml[2 * (w * QH + qh)]);
+    float lt = 0.f, v = 0.f;
     const int c = d >> 6, e = d & 63;
-    float v = 0.f;
 #pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) v += accs[(w * MAXC + c) * 64 + e] * f[w];
-    stf(out, ((int64_t)t * H + h) * Dv + d, v * inv);
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      const float f = expf(ml[2 * (w * QH + qh)] - mt);
+      lt += ml[2 * (w * QH + qh) + 1] * f;
+      v += accs[((w * QH + qh) * MAXC + c) * 64 + e] * f;
+    }
+    stf(out, ((int64_t)t * H + h0 + qh) * Dv + d, v / lt);
   }
 }
 
@@ -207,18 +260,29 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   B200_REQUIRE(Dv >= 1 && Dv <= 256 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..256", D, Dv);
   if (T <= 0) return B200_OK;
   B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
-  dim3 grid((unsigned)(T * H));
+  const int rep = H / G;  // query heads per kv head; the CTA serves 4, 2 or 1 of them with one pass over the keys
+  int QHr = rep % 4 == 0 ? 4 : rep % 2 == 0 ? 2 : 1;
+  while (QHr > 1 && (int64_t)T * (H / QHr) < 4 * 148) QHr /= 2;  // small steps: keep four CTAs per SM before sharing key rows
+  dim3 grid((unsigned)(T * (H / QHr)));
   cudaStream_t st = (cudaStream_t)stream;
-#define ATT_LAUNCH(MC)                                                                                                      \
-  B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC>, grid, dim3(ATT_WARPS * 32),                                      \
-                             (size_t)(D + ATT_WARPS * 64 * MC + 2 * ATT_WARPS) * 4, st, q, ldq, (const KT*)k_pool,         \
-                             (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, window, (KT*)out, T, H, G, \
-                             D, Dv, block_size))
+  const int Dp = (D + 3) & ~3;
+#define ATT_LAUNCH_Q(MC, QH)                                                                                                 \
+  B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32),                                   \
+                             (size_t)(QH * Dp + ATT_WARPS * QH * 64 * MC + 2 * ATT_WARPS * QH) * 4, st, q, ldq,             \
+                             (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale,   \
+                             window, (KT*)out, T, H, G, D, Dv, block_size))
+#define ATT_LAUNCH(MC)                \
+  do {                                \
+    if (QHr == 4) ATT_LAUNCH_Q(MC, 4); \
+    else if (QHr == 2) ATT_LAUNCH_Q(MC, 2); \
+    else ATT_LAUNCH_Q(MC, 1);          \
+  } while (0)
   B200_DISPATCH_ELEM(kv_dtype, KT, {
     if (Dv <= 64) ATT_LAUNCH(1);
     else if (Dv <= 128) ATT_LAUNCH(2);
     else ATT_LAUNCH(4);
   });
+#undef ATT_LAUNCH_Q
 #undef ATT_LAUNCH
   return B200_OK;
 }

@@ -3,7 +3,8 @@
 // from the per-head sink (running maximum = sink, denominator = 1, no value) -- computed FlashAttention-style.
 //   CTA = 64 consecutive new tokens of one sequence x one query head, 4 warps x 16 rows.  Keys are walked in tiles of 32
 //   from the first key the tile's first row may see to the last key its last row may see; each tile's K and V rows are
-//   gathered page by page into shared memory (rows padded by 16 bytes: conflict-free ldmatrix), S = Q K^T and O += P V run
+//   gathered page by page into shared memory with cp.async, one tile ahead of the MMAs (rows padded by 16 bytes:
+//   conflict-free ldmatrix), S = Q K^T and O += P V run
 //   on mma.sync m16n8k16 (bf16 in, fp32 accumulate); the mask is applied per element, the online softmax is fp32.
 // Needs D % 16 == 0 and Dv % 16 == 0, Dv <= 256; other shapes, fp32 pools and decode-sized steps use the warp kernel.
 #include <math.h>
@@ -14,6 +15,18 @@ namespace b200 {
 
 constexpr int PF_ROWS = 64;
 constexpr int PF_KEYS = 32;
+constexpr int PF_STAGES = 2;  // K / V tiles in flight: the next tile's cp.async copies run under the current tile's MMAs
+
+// 16-byte asynchronous global -> shared copy; `ok` false writes zeros (source size 0) and reads nothing
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool ok) {
+  const int n = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
 
 template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
 __global__ void __launch_bounds__(128)
@@ -30,8 +43,8 @@ __global__ void __launch_bounds__(128)
   extern __shared__ __align__(16) unsigned char smraw[];
   const int ldk = D + 8, ldv = Dv + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [64][ldk]
-  __nv_bfloat16* Ks = Qs + PF_ROWS * ldk;                       // [32][ldk]
-  __nv_bfloat16* Vs = Ks + PF_KEYS * ldk;                       // [32][ldv]
+  __nv_bfloat16* Ks0 = Qs + PF_ROWS * ldk;                      // [PF_STAGES][32][ldk]
+  __nv_bfloat16* Vs0 = Ks0 + PF_STAGES * PF_KEYS * ldk;         // [PF_STAGES][32][ldv]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = h / (H / G);
   const int pos0 = seq_pos0[sq];
@@ -59,23 +72,33 @@ __global__ void __launch_bounds__(128)
   const int j_lo = first_pos - window + 1 > 0 ? first_pos - window + 1 : 0;
   const int j_hi = first_pos + last_row;  // inclusive
   const int kch = D / 8, vch = Dv / 8;    // 16-byte chunks per row
-  for (int j0 = (j_lo / PF_KEYS) * PF_KEYS; j0 <= j_hi; j0 += PF_KEYS) {
-    __syncthreads();  // everyone is done with the previous tile (and, first time, Q is written)
+  // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros
+  auto issue = [&](int j0, int st) {
+    __nv_bfloat16* Kd = Ks0 + st * PF_KEYS * ldk;
+    __nv_bfloat16* Vd = Vs0 + st * PF_KEYS * ldv;
     for (int i = tid; i < PF_KEYS * (kch + vch); i += 128) {
       const int r = i / (kch + vch), c = i - r * (kch + vch);
       const int j = j0 + r;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      int64_t row = -1;
-      if (j <= j_hi) row = ((int64_t)bt[j / bs] * G + g) * bs + (j % bs);
-      if (c < kch) {
-        if (row >= 0) val = *reinterpret_cast<const uint4*>(k_pool + row * D + c * 8);
-        *reinterpret_cast<uint4*>(Ks + r * ldk + c * 8) = val;
-      } else {
-        if (row >= 0) val = *reinterpret_cast<const uint4*>(v_pool + row * Dv + (c - kch) * 8);
-        *reinterpret_cast<uint4*>(Vs + r * ldv + (c - kch) * 8) = val;
-      }
+      const bool ok = j <= j_hi;
+      const int64_t row = ok ? ((int64_t)bt[j / bs] * G + g) * bs + (j % bs) : 0;
+      if (c < kch) cp_async16(smem_u32(Kd + r * ldk + c * 8), k_pool + row * D + c * 8, ok);
+      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + row * Dv + (c - kch) * 8, ok);
     }
-    __syncthreads();
+    cp_async_commit();
+  };
+  const int j_first = (j_lo / PF_KEYS) * PF_KEYS;
+  issue(j_first, 0);
+  for (int j0 = j_first, it = 0; j0 <= j_hi; j0 += PF_KEYS, ++it) {
+    const int st = it % PF_STAGES;
+    if (j0 + PF_KEYS <= j_hi) {
+      issue(j0 + PF_KEYS, (it + 1) % PF_STAGES);  // that stage was released by the barrier that ended the previous tile
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();  // this tile's copies of every thread have landed (and, first time, Q is written)
+    const __nv_bfloat16* Ks = Ks0 + st * PF_KEYS * ldk;
+    const __nv_bfloat16* Vs = Vs0 + st * PF_KEYS * ldv;
     // ---- S = Q K^T: 16 rows x 32 keys per warp
     float s[4][4];
 #pragma unroll
@@ -150,6 +173,7 @@ __global__ void __launch_bounds__(128)
         }
       }
     }
+    __syncthreads();  // everyone is done with this stage before the tile after next is copied into it
   }
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -189,7 +213,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
   }
   if (B <= 0 || max_new <= 0) return B200_OK;
   dim3 grid((max_new + PF_ROWS - 1) / PF_ROWS, H, B);
-  const size_t smem = ((size_t)(PF_ROWS + PF_KEYS) * (D + 8) + (size_t)PF_KEYS * (Dv + 8)) * 2;
+  const size_t smem = ((size_t)(PF_ROWS + PF_STAGES * PF_KEYS) * (D + 8) + (size_t)PF_STAGES * PF_KEYS * (Dv + 8)) * 2;
   cudaStream_t st = (cudaStream_t)stream;
   typedef __nv_bfloat16 BT;
 #define PF_LAUNCH(M)                                                                                                          \
