@@ -350,10 +350,15 @@ int b200_moe_tile_rows(void);
  * *num_tiles.  Needs max_tiles >= ceil(npairs / tile_rows) + E and cap >= max_tiles * tile_rows. */
 int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
                    int32_t* num_tiles, int tile_rows, void* stream);
+/* Prompt-sized bf16 batches: out[r][:] = bf16(weight[pair] * h[pair / top][:]) for row r of the sorted list (pair =
+ * sorted_ids[r]; padding rows become zeros), for the rows of the *num_tiles used tiles of tile_rows rows.  out [cap][W]. */
+int b200_moe_gather_scale(const void* h, int ldh, const int32_t* sorted_ids, int cap, int top, const float* weight,
+                          const int32_t* num_tiles, int tile_rows, void* out, int W, void* stream);
 /* out = A W_e^T, fp32 accumulation.  Dense (sorted_ids NULL): rows 0..M-1, one weight.  Grouped: row tile i belongs to
  * expert tile_expert[i]; row r of the tile list is pair sorted_ids[r]; its A row is pair / gather_div (gather_div > 0,
  * scaled by row_scale[pair]) or r itself; its out row is the pair id (scatter) or r.  glu: w_e = [gate; up] of N rows each
- * and out (dtype) = clamped GLU; else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit). */
+ * and out (dtype) = clamped GLU; else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit).  With
+ * tile_rows = 4 x b200_moe_tile_rows() the rows of A are the list b200_moe_gather_scale wrote (gather_div 0, no row_scale). */
 int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
                         int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
                         int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, int tile_rows, void* stream);

@@ -80,6 +80,7 @@ SIGNATURES = {
     "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _p]),
     "b200_moe_topk": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_moe_tile_rows": (_i, []),
+    "b200_moe_gather_scale": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p]),
     "b200_moe_align": (_i, [_p, _i, _i, _p, _i, _p, _i, _p, _i, _p]),
     "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _f, _i, _p]),
 }

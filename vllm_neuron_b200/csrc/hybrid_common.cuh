@@ -22,6 +22,17 @@ template <>
 __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
 // exact-exponential SiLU (the fp32 serving mode compares at 1e-5; common.cuh's silu_f32 is the fast-path variant)
+// 16-byte asynchronous global -> shared copy; `ok` false writes zeros (source size 0) and reads nothing
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool ok) {
+  const int n = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
 // element-type dispatch: `dt` is B200_BF16 or B200_F32

@@ -332,6 +332,167 @@ __global__ void __launch_bounds__(128)
     }
 }
 
+// Prompt-sized bf16 batches.  moe_gather_scale_kernel lays the (token, choice) pairs out in sorted order ONCE, each row
+// scaled by its routing weight in fp32 and rounded to the bf16 operand (padding rows are zeros), so that the expert GEMMs
+// read plain contiguous rows; grouped_mma_pipe_kernel then runs 128 rows x 128 weight rows per CTA (8 warps, 64 x 32 each)
+// with both operands copied by cp.async through a 4-stage ring of K = 32 slices: no register staging, three slices in
+// flight under the MMAs.  Same K order per row as the 32-row kernel: the results are bit-identical.
+__global__ void moe_gather_scale_kernel(const __nv_bfloat16* __restrict__ h, int ldh, const int32_t* __restrict__ sorted_ids,
+                                        int top, const float* __restrict__ weight, const int32_t* __restrict__ num_tiles,
+                                        int tile_rows, __nv_bfloat16* __restrict__ out, int W) {
+  griddep_launch();
+  griddep_wait();
+  const int r = blockIdx.x;
+  if (r >= *num_tiles * tile_rows) return;
+  const int id = sorted_ids[r];
+  const float sc = id >= 0 ? weight[id] : 0.f;
+  const __nv_bfloat16* src = h + (int64_t)(id >= 0 ? id / top : 0) * ldh;
+  for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (id >= 0) {
+      v = *reinterpret_cast<const uint4*>(src + c);
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h2[i]);
+        h2[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (int64_t)r * W + c) = v;
+  }
+}
+
+constexpr int GP_BM = MOE_BM * MOE_WIDE;
+constexpr int GP_STAGES = 4;
+constexpr int GP_THREADS = 256;
+constexpr int GP_STAGE_ELEMS = (GP_BM + GM_WROWS) * GM_LD;
+
+template <int EPI>
+__global__ void __launch_bounds__(GP_THREADS)
+    grouped_mma_pipe_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids,
+                            const __nv_bfloat16* __restrict__ w, int64_t w_stride, const int32_t* __restrict__ tile_expert,
+                            const int32_t* __restrict__ num_tiles, int N, int K, void* __restrict__ out, int ldo, int scatter,
+                            float limit) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ __align__(16) unsigned char gp_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(gp_smem);                             // [stages][A 128 | W 128][GM_LD]
+  int32_t* oid = reinterpret_cast<int32_t*>(gp_smem + (size_t)GP_STAGES * GP_STAGE_ELEMS * 2);  // [128]
+  const int tile = blockIdx.x;
+  if (tile >= *num_tiles) return;
+  const int e = tile_expert[tile];
+  const __nv_bfloat16* we = w + (int64_t)e * w_stride;
+  constexpr int BN = EPI == GL_EPI_GLU ? 64 : 128;  // outputs per CTA
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wn = warp & 3;  // 2 x 4 warps: 64 rows x (32 outputs | 16 gate + 16 up)
+  if (tid < GP_BM) {
+    const int id = sorted_ids[tile * GP_BM + tid];
+    oid[tid] = id < 0 ? -1 : (scatter ? id : tile * GP_BM + tid);
+  }
+  // this thread's copies per K slice: 2 of A and 2 of W, 16 bytes each
+  const __nv_bfloat16* src[4];
+  uint32_t dst[4];
+  const int kc = (tid & 3) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (tid + GP_THREADS * (i & 1)) >> 2;  // 0..127
+    if (i < 2) {
+      src[i] = a + (int64_t)(tile * GP_BM + r) * lda + kc;
+      dst[i] = (uint32_t)((r * GM_LD + kc) * 2);
+    } else {
+      int n, grow;
+      if (EPI == GL_EPI_GLU) {
+        n = n0 + (r & 63);
+        grow = (r < 64 ? 0 : N) + n;
+      } else {
+        n = n0 + r;
+        grow = n;
+      }
+      src[i] = n < N ? we + (int64_t)grow * K + kc : nullptr;
+      dst[i] = (uint32_t)(((GP_BM + r) * GM_LD + kc) * 2);
+    }
+  }
+  const uint32_t ring_u32 = smem_u32(ring);
+  auto issue = [&](int kt) {
+    const int k0 = kt * GM_BK;
+    if (k0 < K) {
+      const uint32_t base = ring_u32 + (uint32_t)((kt % GP_STAGES) * GP_STAGE_ELEMS * 2);
+      const bool kin = k0 + kc < K;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = kin && src[i] != nullptr;
+        cp_async16(base + dst[i], ok ? (const void*)(src[i] + k0) : (const void*)a, ok);
+      }
+    }
+    cp_async_commit();  // an empty group past the end keeps the wait counts uniform
+  };
+  float acc[4][4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  // first shared-memory weight row of this warp's n8 tile j
+  auto nrow = [&](int j) { return EPI == GL_EPI_GLU ? (j < 2 ? 16 * wn + 8 * j : 64 + 16 * wn + 8 * (j - 2)) : 32 * wn + 8 * j; };
+  const int KT = (K + GM_BK - 1) / GM_BK;
+#pragma unroll
+  for (int s = 0; s < GP_STAGES - 1; ++s) issue(s);
+  for (int kt = 0; kt < KT; ++kt) {
+    cp_async_wait<GP_STAGES - 2>();  // slice kt has landed (this thread's part)
+    __syncthreads();                 // ... everyone's part; and everyone is done with slice kt - 1, whose stage is refilled next
+    issue(kt + GP_STAGES - 1);
+    const __nv_bfloat16* As = ring + (kt % GP_STAGES) * GP_STAGE_ELEMS;
+    const __nv_bfloat16* Ws = As + GP_BM * GM_LD;
+#pragma unroll
+    for (int kk = 0; kk < GM_BK; kk += 16) {
+      uint32_t bf[2][4];
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {
+        const int mi = lane >> 3;  // matrix of the x4 load: tile 2 jp + mi / 2, k half mi % 2
+        ldmatrix_x4(bf[jp], smem_u32(Ws + (nrow(2 * jp + (mi >> 1)) + (lane & 7)) * GM_LD + kk + (mi & 1) * 8));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t af[4];
+        ldmatrix_x4(af, smem_u32(As + (64 * wm + mt * 16 + (lane & 15)) * GM_LD + kk + (lane >> 4) * 8));
+#pragma unroll
+        for (int jp = 0; jp < 2; ++jp) {
+          mma_bf16_16816(acc[mt][2 * jp], af, bf[jp][0], bf[jp][1]);
+          mma_bf16_16816(acc[mt][2 * jp + 1], af, bf[jp][2], bf[jp][3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = 64 * wm + mt * 16 + (lane >> 2) + (c >= 2 ? 8 : 0);
+      const int dstrow = oid[r];
+      if (dstrow < 0) continue;
+      const int col = 2 * (lane & 3) + (c & 1);
+      if (EPI == GL_EPI_GLU) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + 16 * wn + 8 * j + col;
+          if (n >= N) continue;
+          const float g = fminf(acc[mt][j][c], limit);
+          const float u = fminf(fmaxf(acc[mt][j + 2][c], -limit), limit);
+          ((__nv_bfloat16*)out)[(int64_t)dstrow * ldo + n] = __float2bfloat16_rn(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + 32 * wn + 8 * j + col;
+          if (n < N) ((float*)out)[(int64_t)dstrow * ldo + n] = acc[mt][j][c];
+        }
+      }
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -348,6 +509,17 @@ int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_we
 }
 
 int b200_moe_tile_rows(void) { return MOE_BM; }
+
+int b200_moe_gather_scale(const void* h, int ldh, const int32_t* sorted_ids, int cap, int top, const float* weight,
+                          const int32_t* num_tiles, int tile_rows, void* out, int W, void* stream) {
+  B200_REQUIRE(h && sorted_ids && weight && num_tiles && out, "moe_gather_scale: null pointer");
+  B200_REQUIRE(top >= 1 && W % 8 == 0 && ldh % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)out & 15),
+               "moe_gather_scale: rows of %d bf16 elements (pitch %d) are not 16-byte vectors", W, ldh);
+  if (cap <= 0) return B200_OK;
+  B200_CUDA_OK(launch_kernel(moe_gather_scale_kernel, dim3(cap), dim3(128), 0, (cudaStream_t)stream, (const __nv_bfloat16*)h, ldh,
+                             sorted_ids, top, weight, num_tiles, tile_rows, (__nv_bfloat16*)out, W));
+  return B200_OK;
+}
 
 int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
                    int32_t* num_tiles, int tile_rows, void* stream) {
@@ -384,8 +556,20 @@ int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int g
       if (glu) GM_LAUNCH(GL_EPI_GLU, 1, 64);
       else GM_LAUNCH(GL_EPI_STORE, 1, 128);
     } else {
-      if (glu) GM_LAUNCH(GL_EPI_GLU, MOE_WIDE, 64);
-      else GM_LAUNCH(GL_EPI_STORE, MOE_WIDE, 128);
+      // wide tiles: the operand rows are the gathered, pre-scaled list (one row per sorted pair, no gather and no scale here)
+      B200_REQUIRE(sorted_ids && tile_expert && num_tiles && gather_div == 0 && !row_scale,
+                   "grouped_linear: 128-row tiles read the gathered pair list (b200_moe_gather_scale)");
+      const size_t smem = (size_t)GP_STAGES * GP_STAGE_ELEMS * 2 + GP_BM * 4;
+#define GP_LAUNCH(EPI, BN)                                                                                                     \
+  do {                                                                                                                         \
+    B200_CUDA_OK(cudaFuncSetAttribute(grouped_mma_pipe_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
+    B200_CUDA_OK(launch_kernel(grouped_mma_pipe_kernel<EPI>, dim3(row_tiles, (N + BN - 1) / BN), dim3(GP_THREADS), smem, st,   \
+                               (const BT*)a, lda, sorted_ids, (const BT*)w, w_expert_stride, tile_expert, num_tiles, N, K, out, \
+                               ldo, scatter, limit));                                                                          \
+  } while (0)
+      if (glu) GP_LAUNCH(GL_EPI_GLU, 64);
+      else GP_LAUNCH(GL_EPI_STORE, 128);
+#undef GP_LAUNCH
     }
 #undef GM_LAUNCH
     return B200_OK;

@@ -17,17 +17,6 @@ constexpr int PF_ROWS = 64;
 constexpr int PF_KEYS = 32;
 constexpr int PF_STAGES = 2;  // K / V tiles in flight: the next tile's cp.async copies run under the current tile's MMAs
 
-// 16-byte asynchronous global -> shared copy; `ok` false writes zeros (source size 0) and reads nothing
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool ok) {
-  const int n = ok ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
 template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
 __global__ void __launch_bounds__(128)
     swa_sink_prefill_kernel(const float* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,

@@ -95,6 +95,7 @@ def _floors(cfg, sz, t, keys_per_query, kv_tokens, nseq):
                      t * (2 * c + 4 * s["heads"] + 4 * inner) + 8.0 * nseq * s["heads"] * s["state"] * s["vdim"]),
         "moe_gate_up_glu": (4.0 * pairs * m["ff"] * w, used * 4.0 * m["ff"] * w + t * 2 * w + pairs * 2 * m["ff"]),
         "moe_down": (2.0 * pairs * m["ff"] * w, used * 2.0 * m["ff"] * w + pairs * (2 * m["ff"] + 4 * w)),
+        "moe_gather_scale": (0.0, pairs * w * 4.0),
         "causal_conv_silu": (0.0, t * (4 * c + 2 * c)),
         "gated_group_rmsnorm": (0.0, t * inner * 10.0),
         "dyt_residual": (0.0, t * w * (4 + 4 + 4 + 2.0)),

@@ -825,8 +825,16 @@ def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float
     act = torch.empty((sorted_ids.numel(), ff), dtype=h.dtype, device=h.device)
     out = torch.empty((h.shape[0] * top, width), dtype=torch.float32, device=h.device)
     lib = _cabi.load()
+    if bm > moe_tile_rows():  # prompt-sized: gather and scale the pairs once, then plain rows into the pipelined kernel
+        rows = torch.empty((sorted_ids.numel(), width), dtype=h.dtype, device=h.device)
+        with _k("moe_gather_scale"):
+            check(lib.b200_moe_gather_scale(_ptr(h), h.stride(0), _ptr(sorted_ids), sorted_ids.numel(), top, _ptr(topk_weight),
+                                            _ptr(num_tiles), bm, _ptr(rows), width, _stream()), "b200_moe_gather_scale")
+        a, lda, gdiv, scale = rows, width, 0, 0
+    else:
+        a, lda, gdiv, scale = h, h.stride(0), top, _ptr(topk_weight)
     with _k("moe_gate_up_glu"):
-        check(lib.b200_grouped_linear(_ptr(h), h.stride(0), _ptr(sorted_ids), top, _ptr(topk_weight), _ptr(w_gate_up), ff2 * width,
+        check(lib.b200_grouped_linear(_ptr(a), lda, _ptr(sorted_ids), gdiv, scale, _ptr(w_gate_up), ff2 * width,
                                       _ptr(tile_expert), _ptr(num_tiles), tiles, 0, ff, width, _edt(h), _ptr(act), ff, 0, 1,
                                       float(limit), bm, _stream()), "b200_grouped_linear")
     with _k("moe_down"):
