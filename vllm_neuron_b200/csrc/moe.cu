@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(128)
 // Prompt-sized bf16 batches.  moe_gather_scale_kernel lays the (token, choice) pairs out in sorted order ONCE, each row
 // scaled by its routing weight in fp32 and rounded to the bf16 operand (padding rows are zeros), so that the expert GEMMs
 // read plain contiguous rows; grouped_mma_pipe_kernel then runs 128 rows x 128 weight rows per CTA (8 warps, 64 x 32 each)
-// with both operands copied by cp.async through a 4-stage ring of K = 32 slices: no register staging, three slices in
+// with both operands copied by cp.async through a 3-stage ring of K = 64 slices: no register staging, two slices in
 // flight under the MMAs.  Same K order per row as the 32-row kernel: the results are bit-identical.
 __global__ void moe_gather_scale_kernel(const __nv_bfloat16* __restrict__ h, int ldh, const int32_t* __restrict__ sorted_ids,
                                         int top, const float* __restrict__ weight, const int32_t* __restrict__ num_tiles,
@@ -363,9 +363,12 @@ __global__ void moe_gather_scale_kernel(const __nv_bfloat16* __restrict__ h, int
 }
 
 constexpr int GP_BM = MOE_BM * MOE_WIDE;
-constexpr int GP_STAGES = 4;
+constexpr int GP_STAGES = 3;
 constexpr int GP_THREADS = 256;
-constexpr int GP_STAGE_ELEMS = (GP_BM + GM_WROWS) * GM_LD;
+constexpr int GP_BK = 64;  // K slice: 128 bytes of every operand row
+constexpr int GP_LD = GP_BK + 8;
+constexpr int GP_CPT = (GP_BM * GP_BK / 8) / GP_THREADS;  // 16-byte copies per thread, operand and slice
+constexpr int GP_STAGE_ELEMS = (GP_BM + GM_WROWS) * GP_LD;
 
 template <int EPI>
 __global__ void __launch_bounds__(GP_THREADS)
@@ -376,7 +379,7 @@ __global__ void __launch_bounds__(GP_THREADS)
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) unsigned char gp_smem[];
-  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(gp_smem);                             // [stages][A 128 | W 128][GM_LD]
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(gp_smem);                             // [stages][A 128 | W 128][GP_LD]
   int32_t* oid = reinterpret_cast<int32_t*>(gp_smem + (size_t)GP_STAGES * GP_STAGE_ELEMS * 2);  // [128]
   const int tile = blockIdx.x;
   if (tile >= *num_tiles) return;
@@ -390,16 +393,16 @@ __global__ void __launch_bounds__(GP_THREADS)
     const int id = sorted_ids[tile * GP_BM + tid];
     oid[tid] = id < 0 ? -1 : (scatter ? id : tile * GP_BM + tid);
   }
-  // this thread's copies per K slice: 2 of A and 2 of W, 16 bytes each
-  const __nv_bfloat16* src[4];
-  uint32_t dst[4];
-  const int kc = (tid & 3) * 8;
+  // this thread's copies per K slice: GP_CPT of A and GP_CPT of W, 16 bytes each
+  const __nv_bfloat16* src[2 * GP_CPT];
+  uint32_t dst[2 * GP_CPT];
+  const int kc = (tid & (GP_BK / 8 - 1)) * 8;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = (tid + GP_THREADS * (i & 1)) >> 2;  // 0..127
-    if (i < 2) {
+  for (int i = 0; i < 2 * GP_CPT; ++i) {
+    const int r = (tid + GP_THREADS * (i % GP_CPT)) / (GP_BK / 8);  // 0..127
+    if (i < GP_CPT) {
       src[i] = a + (int64_t)(tile * GP_BM + r) * lda + kc;
-      dst[i] = (uint32_t)((r * GM_LD + kc) * 2);
+      dst[i] = (uint32_t)((r * GP_LD + kc) * 2);
     } else {
       int n, grow;
       if (EPI == GL_EPI_GLU) {
@@ -410,17 +413,17 @@ __global__ void __launch_bounds__(GP_THREADS)
         grow = n;
       }
       src[i] = n < N ? we + (int64_t)grow * K + kc : nullptr;
-      dst[i] = (uint32_t)(((GP_BM + r) * GM_LD + kc) * 2);
+      dst[i] = (uint32_t)(((GP_BM + r) * GP_LD + kc) * 2);
     }
   }
   const uint32_t ring_u32 = smem_u32(ring);
   auto issue = [&](int kt) {
-    const int k0 = kt * GM_BK;
+    const int k0 = kt * GP_BK;
     if (k0 < K) {
       const uint32_t base = ring_u32 + (uint32_t)((kt % GP_STAGES) * GP_STAGE_ELEMS * 2);
       const bool kin = k0 + kc < K;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < 2 * GP_CPT; ++i) {
         const bool ok = kin && src[i] != nullptr;
         cp_async16(base + dst[i], ok ? (const void*)(src[i] + k0) : (const void*)a, ok);
       }
@@ -436,7 +439,7 @@ __global__ void __launch_bounds__(GP_THREADS)
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
   // first shared-memory weight row of this warp's n8 tile j
   auto nrow = [&](int j) { return EPI == GL_EPI_GLU ? (j < 2 ? 16 * wn + 8 * j : 64 + 16 * wn + 8 * (j - 2)) : 32 * wn + 8 * j; };
-  const int KT = (K + GM_BK - 1) / GM_BK;
+  const int KT = (K + GP_BK - 1) / GP_BK;
 #pragma unroll
   for (int s = 0; s < GP_STAGES - 1; ++s) issue(s);
   for (int kt = 0; kt < KT; ++kt) {
@@ -444,19 +447,19 @@ __global__ void __launch_bounds__(GP_THREADS)
     __syncthreads();                 // ... everyone's part; and everyone is done with slice kt - 1, whose stage is refilled next
     issue(kt + GP_STAGES - 1);
     const __nv_bfloat16* As = ring + (kt % GP_STAGES) * GP_STAGE_ELEMS;
-    const __nv_bfloat16* Ws = As + GP_BM * GM_LD;
+    const __nv_bfloat16* Ws = As + GP_BM * GP_LD;
 #pragma unroll
-    for (int kk = 0; kk < GM_BK; kk += 16) {
+    for (int kk = 0; kk < GP_BK; kk += 16) {
       uint32_t bf[2][4];
 #pragma unroll
       for (int jp = 0; jp < 2; ++jp) {
         const int mi = lane >> 3;  // matrix of the x4 load: tile 2 jp + mi / 2, k half mi % 2
-        ldmatrix_x4(bf[jp], smem_u32(Ws + (nrow(2 * jp + (mi >> 1)) + (lane & 7)) * GM_LD + kk + (mi & 1) * 8));
+        ldmatrix_x4(bf[jp], smem_u32(Ws + (nrow(2 * jp + (mi >> 1)) + (lane & 7)) * GP_LD + kk + (mi & 1) * 8));
       }
 #pragma unroll
       for (int mt = 0; mt < 4; ++mt) {
         uint32_t af[4];
-        ldmatrix_x4(af, smem_u32(As + (64 * wm + mt * 16 + (lane & 15)) * GM_LD + kk + (lane >> 4) * 8));
+        ldmatrix_x4(af, smem_u32(As + (64 * wm + mt * 16 + (lane & 15)) * GP_LD + kk + (lane >> 4) * 8));
 #pragma unroll
         for (int jp = 0; jp < 2; ++jp) {
           mma_bf16_16816(acc[mt][2 * jp], af, bf[jp][0], bf[jp][1]);
