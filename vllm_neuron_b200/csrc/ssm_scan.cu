@@ -11,36 +11,41 @@
 namespace b200 {
 
 constexpr int CONV_MAX_TAPS = 16;
+constexpr int CONV_RUN = 16;  // most consecutive tokens per thread (large steps): the window's earlier inputs and the taps are cache hits
 
-// one thread per (token, channel)
+// one thread per (run of `run` tokens, channel); run = 1 for decode-sized steps
 template <typename OT>
 __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, int col0, const float* __restrict__ cw,
                                         const float* __restrict__ cb, const float* __restrict__ state,
                                         const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_start,
                                         const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos0,
-                                        OT* __restrict__ out, int C, int taps) {
+                                        OT* __restrict__ out, int T, int C, int taps, int run) {
   griddep_launch();
   griddep_wait();
-  const int t = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const int s = tok_seq[t];
-  const int i = t - seq_start[s];  // index inside this step's portion
-  const bool has_state = seq_pos0[s] > 0;
-  const float* st = state + (int64_t)seq_slot[s] * (taps - 1) * C;
-  float acc = cb[c];
-  for (int j = 0; j < taps; ++j) {
-    const int src = i - (taps - 1 - j);  // portion index of the input under tap j (last tap = current token)
-    float v;
-    if (src >= 0)
-      v = in[(int64_t)(t - (taps - 1 - j)) * ld + col0 + c];
-    else if (has_state)
-      v = st[(int64_t)(src + taps - 1) * C + c];
-    else
-      v = 0.f;
-    acc += v * cw[(int64_t)c * taps + j];
+  const float bias = cb[c];
+  const float* wc = cw + (int64_t)c * taps;
+  const int t_end = min(T, (int)(blockIdx.y + 1) * run);
+  for (int t = blockIdx.y * run; t < t_end; ++t) {
+    const int s = tok_seq[t];
+    const int i = t - seq_start[s];  // index inside this step's portion
+    const bool has_state = seq_pos0[s] > 0;
+    const float* st = state + (int64_t)seq_slot[s] * (taps - 1) * C;
+    float acc = bias;
+    for (int j = 0; j < taps; ++j) {
+      const int src = i - (taps - 1 - j);  // portion index of the input under tap j (last tap = current token)
+      float v;
+      if (src >= 0)
+        v = in[(int64_t)(t - (taps - 1 - j)) * ld + col0 + c];
+      else if (has_state)
+        v = st[(int64_t)(src + taps - 1) * C + c];
+      else
+        v = 0.f;
+      acc += v * wc[j];
+    }
+    stf(out, (int64_t)t * C + c, silu_f(acc));
   }
-  stf(out, (int64_t)t * C + c, silu_f(acc));
 }
 
 // new state = the last (taps - 1) inputs of [old state | this step's inputs]; one thread per (sequence, channel) reads
@@ -325,10 +330,11 @@ int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w
   B200_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv_silu: %d taps (1..%d supported)", taps, CONV_MAX_TAPS);
   if (T <= 0 || B <= 0) return B200_OK;
   const int th = 128;
+  const int run = T / 256 < 1 ? 1 : T / 256 > CONV_RUN ? CONV_RUN : T / 256;
   B200_DISPATCH_ELEM(out_dtype, OT,
-                     B200_CUDA_OK(launch_kernel(causal_conv_silu_kernel<OT>, dim3((C + th - 1) / th, T), dim3(th), 0,
+                     B200_CUDA_OK(launch_kernel(causal_conv_silu_kernel<OT>, dim3((C + th - 1) / th, (T + run - 1) / run), dim3(th), 0,
                                                 (cudaStream_t)stream, in, ld, col0, conv_w, conv_b, (const float*)state, tok_seq,
-                                                seq_start, seq_slot, seq_pos0, (OT*)out, C, taps)));
+                                                seq_start, seq_slot, seq_pos0, (OT*)out, T, C, taps, run)));
   if (taps > 1)
     B200_CUDA_OK(launch_kernel(conv_state_update_kernel, dim3((C + th - 1) / th, B), dim3(th), 0, (cudaStream_t)stream, in, ld,
                                col0, state, seq_start, seq_slot, seq_pos0, C, taps));
