@@ -99,7 +99,7 @@ constexpr int SCAN_CHUNK = 32;
 enum { SEG_FIRST = 1, SEG_LAST = 2 };
 
 template <typename XT, int NPT, int PP, bool PARTIAL>
-__global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES)
+__global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES, (NPT * PP <= 32) ? 2 : 1)
     ssd_scan_kernel(const XT* __restrict__ xbc, int C, const float* __restrict__ dt_in, int ld_dt, int dt_col0,
                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
                     float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
@@ -298,7 +298,7 @@ static int launch_scan(const void* xbc, int C, const float* dt_in, int ld_dt, in
   return B200_OK;
 }
 
-// columns per thread: as many as the head has 32-column planes, while the state stays within 64 registers
+// columns per thread: as many as the head has 32-column planes, while the state stays within 32 registers (two CTAs per SM)
 template <typename XT, int NPT>
 static int pick_scan(const void* xbc, int C, const float* dt_in, int ld_dt, int dt_col0, const float* A_log, const float* dt_bias,
                      const float* Dskip, float* state, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
@@ -307,7 +307,7 @@ static int pick_scan(const void* xbc, int C, const float* dt_in, int ld_dt, int 
 #define PICK_ARGS                                                                                                             \
   xbc, C, dt_in, ld_dt, dt_col0, A_log, dt_bias, Dskip, state, seq_start, seq_slot, seq_pos0, y, B, H, P, N, G, segs, num_segs, \
       seq_seg0, seg_state, seg_dtsum, stream
-  if constexpr (NPT * 4 <= 64) {
+  if constexpr (NPT * 4 <= 32) {
     if (P > 64) return launch_scan<XT, NPT, 4>(PICK_ARGS);
   }
   if constexpr (NPT * 2 <= 64) {
