@@ -199,6 +199,28 @@ def test_attention_window_edges_sink_and_pages(chunks):
     _close(_run_attn(q, k, v, sink, window, bs, chunks, torch.bfloat16), want, 3e-2)
 
 
+@pytest.mark.parametrize("H,G,D,Dv", [(8, 2, 24, 40), (4, 2, 32, 16), (6, 2, 20, 70), (16, 4, 64, 136)])
+def test_warp_attention_shares_key_rows_between_query_heads(H, G, D, Dv):
+    """Steps with many tokens on the CUDA-core kernel (fp32 pools; bf16 pools with head sizes the tensor-core kernel does not
+    take): one CTA serves 4 or 2 query heads of a kv head (8/2, 16/4 and 4/2 heads), or 1 (6/2).  A dominant key just inside
+    and just outside the window of the last query, per head."""
+    from oracle.pumopel_ref import sink_window_attention
+
+    T, window, bs = 420, 50, 8
+    for head in (0, H - 1):
+        for j, inside in ((T - window, True), (T - 1 - window, False)):
+            q, k, v, sink = _attn_case(T, H, G, D, Dv, window, bs, spike=(T - 1, j, head))
+            want = sink_window_attention(q.double(), k.double(), v.double(), sink.double(), 1 / math.sqrt(D), window)
+            got = _run_attn(q, k, v, sink, window, bs, [400, 20])
+            _close(got, want, 2e-5)
+            row = got[T - 1].view(H, Dv)[head].cpu()
+            assert ((row - v[j, head // (H // G)]).abs().max() < 1e-3) == inside
+    if D % 16 or Dv % 16:
+        q, k, v, sink = _attn_case(T, H, G, D, Dv, window, bs)
+        want = sink_window_attention(q.double(), k.double(), v.double(), sink.double(), 1 / math.sqrt(D), window)
+        _close(_run_attn(q, k, v, sink, window, bs, [T], torch.bfloat16), want, 3e-2)
+
+
 @pytest.mark.parametrize("chunks", [[150], [16, 64, 3, 67], [33, 1, 1, 17, 98]])
 def test_tensor_core_prompt_attention_edges(chunks):
     """bf16 pools, head sizes 32 / 48: portions of 16 tokens or more run on the mma.sync kernel (64-row tiles, 32-key tiles
