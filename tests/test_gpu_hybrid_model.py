@@ -160,6 +160,47 @@ def test_mixed_batches_with_reused_rows_and_pages(dtype):
             assert d < 1e-5, (i, d)
 
 
+def _random_cfg(rng):
+    """A configuration drawn at random: 2-6 layers in any order, head counts / sizes / windows / taps / expert counts that
+    need not be multiples of anything, some layers without feed-forward, window or value mixing."""
+    heads = rng.choice([2, 4, 6, 8])
+    kv = rng.choice([h for h in (1, 2, 3, 4, 6, 8) if heads % h == 0])
+    dim, vdim = rng.choice([16, 24, 40, 64, 96, 128]), rng.choice([16, 24, 32, 48, 80, 136])
+    sh = rng.choice([2, 4, 6, 12])
+    sg = rng.choice([g for g in (1, 2, 3, 4, 6) if sh % g == 0])
+    sv, sn = rng.choice([16, 33, 48, 64, 80]), rng.choice([16, 24, 48, 64, 96, 130])
+    ng = rng.choice([g for g in (1, 2, 4, sh) if (sh * sv) % g == 0])
+    conv = rng.choice([1, 2, 3, 4])
+    experts, top = rng.choice([(4, 1), (4, 4), (8, 2), (16, 1), (32, 4)])
+    ff, lim, shared = rng.choice([16, 40, 64]), rng.choice([1.0, 1.5, 7.0]), rng.choice([0, 32, 72])
+    layers = []
+    for _ in range(rng.randint(2, 6)):
+        mlp = None if rng.random() < 0.15 else _moe(experts, top, ff, lim, shared or None)
+        if rng.random() < 0.5:
+            layers.append(_layer("mamba2", mlp, heads=sh, vdim=sv, state=sn, groups=sg, conv=conv, norm_groups=ng))
+        else:
+            m = dict(heads=heads, kv_heads=kv, dim=dim, vdim=vdim, scale=rng.choice([dim ** -0.5, 0.1, 0.3]), v_mix=rng.random() < 0.8)
+            if rng.random() < 0.85:
+                m["mask"] = {"size": rng.choice([1, 2, 17, 64, 100, 200])}
+            layers.append(_layer("attention", mlp, **m))
+    return {"architecture": "Pumopel", "vocab": rng.choice([100, 257, 512]), "width": rng.choice([64, 96, 136, 192, 256]),
+            "norm": {"eps": rng.choice([1e-6, 1e-5])}, "embedding": {"scale": rng.choice([0.5, 1.0, 2.0])}, "layers": layers}
+
+
+@pytest.mark.parametrize("seed", [2, 5, 12, 19, 22])
+def test_random_configurations_in_32_bit(seed):
+    """Whole prompt (long enough for the segmented scan and the wide expert tiles), ragged portions and a mixed batch of a
+    prompt beside a decoding request, for configurations nobody picked by hand."""
+    import random
+
+    c = Case(_random_cfg(random.Random(seed)), "float32", seed=seed, max_num_seqs=3, pool_tokens=1024)
+    toks, short = c.tokens(420, 50 + seed), c.tokens(30, 60 + seed)
+    c.check(c.replay({"w": toks}, [[("w", 420)]]), {"w": toks})
+    c.check(c.replay({"p": toks}, [[("p", n)] for n in _portions(420, [2, 3, 130, 1, 33, 7, 64, 1, 1, 257])]), {"p": toks})
+    mixed = c.replay({"a": toks, "b": short}, [[("a", 300), ("b", 1)]] + [[("a", 1), ("b", 1)] for _ in range(29)] + [[("a", 91)]])
+    c.check(mixed, {"a": toks, "b": short})
+
+
 def test_long_decoding_past_every_window():
     c = Case(cfg_a(), "float32", max_num_seqs=2, pool_tokens=512)
     toks = c.tokens(300, 3)
