@@ -38,7 +38,7 @@ __global__ void kv_write_vmix_kernel(const float* __restrict__ qkv, int ld, int 
   }
 }
 
-constexpr int ATT_WARPS = 4;
+constexpr int ATT_WARPS = 16;  // the launch is bound by load latency: every warp walks few key tiles, many are in flight
 
 // QH query rows (fp32, shared memory, pitch D) . one k row, with 16-byte loads when the row allows it: the key row is
 // fetched once for all the query heads of its group that the CTA serves
@@ -112,7 +112,7 @@ __device__ __forceinline__ float2 ld_pair(const __nv_bfloat16* r, int d, int Dv,
   return make_float2(d < Dv ? __bfloat162float(r[d]) : 0.f, d + 1 < Dv ? __bfloat162float(r[d + 1]) : 0.f);
 }
 
-// One CTA per (token, QH query heads that share a kv head): its 4 warps take the window's 32-key tiles round-robin
+// One CTA per (token, QH query heads that share a kv head): its 16 warps take the window's 32-key tiles round-robin
 // (lane-per-key scores, lanes-over-columns value accumulation, each warp its own running maximum / denominator /
 // accumulator per head) and merge through shared memory.  Every K and V row is fetched once for the QH heads.  Warp 0
 // carries the sink's 1 in the denominators.  The split depends on the position and the window only.
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       }
     }
   }
-  // ---- merge the warps (fixed order 0..3)
+  // ---- merge the warps (fixed order)
 #pragma unroll
   for (int qh = 0; qh < QH; ++qh) {
 #pragma unroll
@@ -262,15 +262,20 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
   const int rep = H / G;  // query heads per kv head; the CTA serves 4, 2 or 1 of them with one pass over the keys
   int QHr = rep % 4 == 0 ? 4 : rep % 2 == 0 ? 2 : 1;
-  while (QHr > 1 && (int64_t)T * (H / QHr) < 4 * 148) QHr /= 2;  // small steps: keep four CTAs per SM before sharing key rows
+  while (QHr > 1 && (int64_t)T * (H / QHr) < 148) QHr /= 2;  // small steps: keep a CTA per SM before sharing key rows
   dim3 grid((unsigned)(T * (H / QHr)));
   cudaStream_t st = (cudaStream_t)stream;
   const int Dp = (D + 3) & ~3;
 #define ATT_LAUNCH_Q(MC, QH)                                                                                                 \
-  B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32),                                   \
-                             (size_t)(QH * Dp + ATT_WARPS * QH * 64 * MC + 2 * ATT_WARPS * QH) * 4, st, q, ldq,             \
-                             (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale,   \
-                             window, (KT*)out, T, H, G, D, Dv, block_size))
+  do {                                                                                                                       \
+    const size_t smem = (size_t)(QH * Dp + ATT_WARPS * QH * 64 * MC + 2 * ATT_WARPS * QH) * 4;                               \
+    if (smem > 48 * 1024)                                                                                                    \
+      B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_attn_kernel<KT, MC, QH>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                        (int)smem));                                                                         \
+    B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq,               \
+                               (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, \
+                               window, (KT*)out, T, H, G, D, Dv, block_size));                                               \
+  } while (0)
 #define ATT_LAUNCH(MC)                \
   do {                                \
     if (QHr == 4) ATT_LAUNCH_Q(MC, 4); \

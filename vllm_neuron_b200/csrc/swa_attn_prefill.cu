@@ -15,7 +15,8 @@ namespace b200 {
 
 constexpr int PF_ROWS = 64;
 constexpr int PF_KEYS = 32;
-constexpr int PF_STAGES = 2;  // K / V tiles in flight: the next tile's cp.async copies run under the current tile's MMAs
+constexpr int PF_STAGES = 2;  // ring of K / V tiles: the next tile's cp.async copies run under the current tile's MMAs (a third
+                              // stage costs a resident CTA per SM and measured slower)
 
 template <int DV16M>  // accumulator capacity: Dv <= 16 * DV16M
 __global__ void __launch_bounds__(128)
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(128)
   auto issue = [&](int j0, int st) {
     __nv_bfloat16* Kd = Ks0 + st * PF_KEYS * ldk;
     __nv_bfloat16* Vd = Vs0 + st * PF_KEYS * ldv;
-    for (int i = tid; i < PF_KEYS * (kch + vch); i += 128) {
+    for (int i = tid; j0 <= j_hi && i < PF_KEYS * (kch + vch); i += 128) {
       const int r = i / (kch + vch), c = i - r * (kch + vch);
       const int j = j0 + r;
       const bool ok = j <= j_hi;
@@ -73,18 +74,16 @@ __global__ void __launch_bounds__(128)
       if (c < kch) cp_async16(smem_u32(Kd + r * ldk + c * 8), k_pool + row * D + c * 8, ok);
       else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + row * Dv + (c - kch) * 8, ok);
     }
-    cp_async_commit();
+    cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
   const int j_first = (j_lo / PF_KEYS) * PF_KEYS;
-  issue(j_first, 0);
+#pragma unroll
+  for (int s = 0; s < PF_STAGES - 1; ++s) issue(j_first + s * PF_KEYS, s);
   for (int j0 = j_first, it = 0; j0 <= j_hi; j0 += PF_KEYS, ++it) {
     const int st = it % PF_STAGES;
-    if (j0 + PF_KEYS <= j_hi) {
-      issue(j0 + PF_KEYS, (it + 1) % PF_STAGES);  // that stage was released by the barrier that ended the previous tile
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    // refill the stage that the barrier at the end of the previous tile released, then wait for this tile's group
+    issue(j0 + (PF_STAGES - 1) * PF_KEYS, (it + PF_STAGES - 1) % PF_STAGES);
+    cp_async_wait<PF_STAGES - 1>();
     __syncthreads();  // this tile's copies of every thread have landed (and, first time, Q is written)
     const __nv_bfloat16* Ks = Ks0 + st * PF_KEYS * ldk;
     const __nv_bfloat16* Vs = Vs0 + st * PF_KEYS * ldv;
