@@ -79,8 +79,9 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
 }
 
 // Selective scan.  CTA = (32 PP value columns p of one head) x (8 slices of the state dimension); thread (pl, s) keeps
-// S[p][n] for p = p0 + pl + 32 q (q < PP) and n = s, s + 8, ... (NPT of them) in registers across the tokens it walks, so
-// one B / C element read from shared memory serves PP columns; y is reduced over the 8 slices with shuffles.  Tokens are
+// S[p][n] for p = p0 + pl + 32 q (q < PP) and the pairs n = 2 s + 16 k + {0, 1} (NPT elements) in registers across the tokens it walks, so
+// one B / C pair read from shared memory serves PP columns and the update runs on packed fp32 pairs (two state elements
+// per issue slot); y is reduced over the 8 slices with shuffles.  Tokens are
 // walked in chunks of SCAN_CHUNK: the CTA stages the chunk's B, C and x rows in shared memory with coalesced loads
 // (fetched into registers one chunk ahead) and computes each token's step size and decay ONCE (softplus / exp are not
 // repeated by every thread), then the recurrence runs out of shared memory.  State layout [slots][H][P][N]: the 8 slices
@@ -93,6 +94,24 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
 //      + S_loc[k], S_in[0] = the slot's state (zero at position 0), and stores S_in[k] over the scratch;
 //   3. the full launch starts every segment from its S_in, writes y, and the last segment writes the slot's new state.
 // The recurrence is linear in S, so this is the sequential result up to fp32 rounding; everything stays fp32.
+// packed fp32 pairs (sm_100 fma.rn.f32x2 / mul.rn.f32x2): two IEEE fp32 operations per issue slot, each lane rounded exactly
+// like the scalar instruction
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 constexpr int SCAN_PLANES = 32;
 constexpr int SCAN_SLICES = 8;
 constexpr int SCAN_CHUNK = 32;
@@ -140,14 +159,16 @@ __global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES, (NPT * PP <= 32) ? 2
     else S_in = seg_state + ((int64_t)blockIdx.z * H + h) * head_elems;
     if (flags & SEG_LAST) S_out = slot;
   }
-  float S[PP][NPT];
+  // thread (pl, s) owns the state pairs n = 2 s + 16 k + {0, 1}, k < NPT / 2, of each of its columns
+  float2 S[PP][NPT / 2];
 #pragma unroll
   for (int q = 0; q < PP; ++q) {
     const int p = p0 + pl + SCAN_PLANES * q;
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int n = s + i * SCAN_SLICES;
-      S[q][i] = (S_in && p < P && n < N) ? S_in[(int64_t)p * N + n] : 0.f;
+    for (int k = 0; k < NPT / 2; ++k) {
+      const int n = 2 * s + 2 * SCAN_SLICES * k;
+      S[q][k].x = (S_in && p < P && n < N) ? S_in[(int64_t)p * N + n] : 0.f;
+      S[q][k].y = (S_in && p < P && n + 1 < N) ? S_in[(int64_t)p * N + n + 1] : 0.f;
     }
   }
   const float negA = -expf(A_log[h]), bias = dt_bias[h], dsk = Dskip[h];
@@ -196,29 +217,31 @@ __global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES, (NPT * PP <= 32) ? 2
     if (c0 + SCAN_CHUNK < t1) fetch(c0 + SCAN_CHUNK);
     for (int tok = 0; tok < nc; ++tok) {
       const float a = dec[tok], dtv = dts[tok];
-      float xc[PP], dx[PP], acc[PP];
+      const float2 a2 = make_float2(a, a);
+      float xc[PP];
+      float2 dx2[PP], acc2[PP];
 #pragma unroll
       for (int q = 0; q < PP; ++q) {
         xc[q] = xs[tok * PC + pl + SCAN_PLANES * q];
-        dx[q] = dtv * xc[q];
-        acc[q] = 0.f;
+        dx2[q] = make_float2(dtv * xc[q], dtv * xc[q]);
+        acc2[q] = make_float2(0.f, 0.f);
       }
-      const float* Br = Bs + tok * NP + s;
-      const float* Cr = Cs + tok * NP + s;
+      const float* Br = Bs + tok * NP + 2 * s;
+      const float* Cr = Cs + tok * NP + 2 * s;
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const float bv = Br[i * SCAN_SLICES];
-        const float cv = PARTIAL ? 0.f : Cr[i * SCAN_SLICES];
+      for (int k = 0; k < NPT / 2; ++k) {
+        const float2 b2 = *reinterpret_cast<const float2*>(Br + 2 * SCAN_SLICES * k);
+        const float2 c2 = PARTIAL ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(Cr + 2 * SCAN_SLICES * k);
 #pragma unroll
         for (int q = 0; q < PP; ++q) {
-          S[q][i] = a * S[q][i] + bv * dx[q];
-          if (!PARTIAL) acc[q] += S[q][i] * cv;
+          S[q][k] = ffma2(a2, S[q][k], fmul2(b2, dx2[q]));
+          if (!PARTIAL) acc2[q] = ffma2(S[q][k], c2, acc2[q]);
         }
       }
       if (!PARTIAL) {
 #pragma unroll
         for (int q = 0; q < PP; ++q) {
-          float v = acc[q];
+          float v = acc2[q].x + acc2[q].y;
           v += __shfl_xor_sync(0xffffffffu, v, 1);
           v += __shfl_xor_sync(0xffffffffu, v, 2);
           v += __shfl_xor_sync(0xffffffffu, v, 4);
@@ -233,9 +256,10 @@ __global__ void __launch_bounds__(SCAN_PLANES* SCAN_SLICES, (NPT * PP <= 32) ? 2
     for (int q = 0; q < PP; ++q) {
       const int p = p0 + pl + SCAN_PLANES * q;
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const int n = s + i * SCAN_SLICES;
-        if (p < P && n < N) S_out[(int64_t)p * N + n] = S[q][i];
+      for (int k = 0; k < NPT / 2; ++k) {
+        const int n = 2 * s + 2 * SCAN_SLICES * k;
+        if (p < P && n < N) S_out[(int64_t)p * N + n] = S[q][k].x;
+        if (p < P && n + 1 < N) S_out[(int64_t)p * N + n + 1] = S[q][k].y;
       }
     }
   }
