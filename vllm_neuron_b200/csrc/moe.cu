@@ -14,7 +14,7 @@
 namespace b200 {
 
 constexpr int MOE_BM = 32;
-constexpr int MOE_WIDE = 4;  // prompt-sized batches: tiles of MOE_BM * MOE_WIDE rows (tensor-core kernel only)
+constexpr int MOE_WIDE = 4;  // prompt-sized bf16 batches: tiles of MOE_BM * MOE_WIDE rows (grouped_mma_pipe_kernel)
 constexpr int GL_BN = 64;
 constexpr int GL_BK = 16;
 constexpr int GL_THREADS = 256;
@@ -182,7 +182,7 @@ constexpr int GM_BK = 32;
 constexpr int GM_LD = GM_BK + 8;
 constexpr int GM_WROWS = 128;
 
-template <int EPI, int R>
+template <int EPI>
 __global__ void __launch_bounds__(128)
     grouped_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
                        const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ w, int64_t w_stride,
@@ -190,7 +190,8 @@ __global__ void __launch_bounds__(128)
                        void* __restrict__ out, int ldo, int scatter, float limit) {
   griddep_launch();
   griddep_wait();
-  constexpr int BM = MOE_BM * R;  // rows per tile: R sub-tiles of 32 share every weight tile
+  constexpr int R = 1;            // 32-row sub-tiles per CTA (prompt-sized batches take grouped_mma_pipe_kernel instead)
+  constexpr int BM = MOE_BM * R;  // rows per tile
   __shared__ __align__(16) __nv_bfloat16 As[BM][GM_LD];
   __shared__ __align__(16) __nv_bfloat16 Ws[GM_WROWS][GM_LD];
   __shared__ int32_t rid[BM];
@@ -551,13 +552,13 @@ int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int g
                "grouped_linear: %d rows per tile (32, or 128 for 16-byte aligned bf16 operands)", tile_rows);
   if (mma_ok) {
     using BT = __nv_bfloat16;
-#define GM_LAUNCH(EPI, R, BN)                                                                                                \
-  B200_CUDA_OK(launch_kernel(grouped_mma_kernel<EPI, R>, dim3(row_tiles, (N + BN - 1) / BN), dim3(128), 0, st, (const BT*)a, lda, \
+#define GM_LAUNCH(EPI, BN)                                                                                                   \
+  B200_CUDA_OK(launch_kernel(grouped_mma_kernel<EPI>, dim3(row_tiles, (N + BN - 1) / BN), dim3(128), 0, st, (const BT*)a, lda, \
                              sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N, K, \
                              out, ldo, scatter, limit))
     if (tile_rows == MOE_BM) {
-      if (glu) GM_LAUNCH(GL_EPI_GLU, 1, 64);
-      else GM_LAUNCH(GL_EPI_STORE, 1, 128);
+      if (glu) GM_LAUNCH(GL_EPI_GLU, 64);
+      else GM_LAUNCH(GL_EPI_STORE, 128);
     } else {
       // wide tiles: the operand rows are the gathered, pre-scaled list (one row per sorted pair, no gather and no scale here)
       B200_REQUIRE(sorted_ids && tile_expert && num_tiles && gather_div == 0 && !row_scale,
