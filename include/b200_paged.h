@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 9
+#define B200_ABI_VERSION 10
 
 enum {
   B200_OK = 0,
@@ -46,6 +46,9 @@ enum {
 
 /* B200_INT8_WO is only valid as a GEMM `ab_dtype`: bf16 activations x int8 weights (weight-only quantisation) */
 enum { B200_BF16 = 0, B200_FP8_E4M3 = 1, B200_INT8 = 2, B200_F32 = 3, B200_INT8_WO = 4 };
+/* gate activations of a gated-linear unit, and how a router turns its chosen logits into weights */
+enum { B200_ACT_SWISH_CLAMPED = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2 };
+enum { B200_ROUTE_SIGMOID = 0, B200_ROUTE_SOFTMAX_TOP = 1 };
 
 int b200_abi_version(void);
 const char* b200_last_error(void);
@@ -307,7 +310,8 @@ int b200_gated_group_rmsnorm(const float* y, const float* z, int ldz, const floa
 /* gate_up fp32 [T][2 ff] (gate first): a = min(gate, L), b = max(-L, min(up, L)), out = (b + 1) * a / (1 + exp(-1.702 a)) */
 int b200_clamped_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, float limit, void* stream);
 /* Causal depthwise convolution + SiLU over columns [col0, col0 + C) of `in` (fp32, pitch ld); conv_w fp32 [C][taps] with
- * the LAST tap on the current token; state fp32 [slots][taps - 1][C] holds each sequence's last inputs and is updated. */
+ * the LAST tap on the current token; conv_b fp32 [C] or NULL; state fp32 [slots][taps - 1][C] holds each sequence's last
+ * inputs and is updated. */
 int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
                           const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                           void* out, int out_dtype, int T, int B, int C, int taps, void* stream);
@@ -327,22 +331,27 @@ int b200_ssd_scan(const void* xbc, int x_dtype, int C, const float* dt_in, int l
 int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* v_first, float lambda, int mode, void* k_pool,
                        void* v_pool, int kv_dtype, const int64_t* slot_mapping, int T, int G, int D, int Dv, int block_size,
                        void* stream);
-/* Sliding-window attention with a per-head sink logit in the softmax denominator, no positional rotation.
+/* Sliding-window attention with a per-head sink logit in the softmax denominator (sink NULL: ordinary softmax), scores
+ * taken as they are (a rotation, if any, is already in q and the cached keys).
  * q fp32 rows (pitch ldq, head h at column h * D); token t is position tok_pos[t] of the sequence whose block-table row is
- * tok_row[t] and sees keys j with 0 <= pos - j < window, all already in the pools.  out [T][H][Dv] in kv_dtype. */
+ * tok_row[t] and sees keys j with 0 <= pos - j < window, all already in the pools.  Value rows have pitch v_pitch >= Dv
+ * (v_pool may be k_pool itself, with the values in the leading columns of the key rows).  out [T][H][Dv] in kv_dtype.
+ * Dv <= 512. */
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
-                       int window, void* out, int T, int H, int G, int D, int Dv, int block_size, void* stream);
+                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, void* stream);
 /* The same attention for prompt portions on the tensor cores (bf16 pools; D and Dv multiples of 16, Dv <= 256, else
  * B200_ERR_UNSUPPORTED): sequence s brings tokens [seq_start[s], seq_start[s+1]) at positions seq_pos0[s].., block-table row
  * seq_slot[s]; max_new = the longest portion of the step.  q is rounded to bf16; softmax and accumulation are fp32. */
 int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
-                               int Dv, int block_size, void* stream);
-/* Router decision over fp32 logits [T] rows of pitch ld: the `top` largest (ties to the lower index); weights = sigmoid of
- * the chosen logits (no renormalisation). */
-int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_weight, int T, int E, int top, void* stream);
+                               int Dv, int v_pitch, int block_size, void* stream);
+/* Router decision over fp32 logits [T] rows of pitch ld (+ bias fp32 [E] when given): the `top` largest (ties to the lower
+ * index); weights = sigmoid of each chosen logit, no renormalisation (B200_ROUTE_SIGMOID), or the softmax over the chosen
+ * logits only (B200_ROUTE_SOFTMAX_TOP). */
+int b200_moe_topk(const float* logits, int ld, const float* bias, int mode, int32_t* topk_idx, float* topk_weight, int T, int E,
+                  int top, void* stream);
 /* rows per expert tile of b200_moe_align / b200_grouped_linear; four times as many (tile_rows = 4 x this) are taken for
  * prompt-sized batches of 16-byte aligned bf16 operands, where every weight tile then serves 128 rows */
 int b200_moe_tile_rows(void);
@@ -351,17 +360,69 @@ int b200_moe_tile_rows(void);
 int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_ids, int cap, int32_t* tile_expert, int max_tiles,
                    int32_t* num_tiles, int tile_rows, void* stream);
 /* Prompt-sized bf16 batches: out[r][:] = bf16(weight[pair] * h[pair / top][:]) for row r of the sorted list (pair =
- * sorted_ids[r]; padding rows become zeros), for the rows of the *num_tiles used tiles of tile_rows rows.  out [cap][W]. */
+ * sorted_ids[r]; padding rows become zeros; weight NULL: plain copies), for the rows of the *num_tiles used tiles of
+ * tile_rows rows.  out [cap][W]. */
 int b200_moe_gather_scale(const void* h, int ldh, const int32_t* sorted_ids, int cap, int top, const float* weight,
                           const int32_t* num_tiles, int tile_rows, void* out, int W, void* stream);
 /* out = A W_e^T, fp32 accumulation.  Dense (sorted_ids NULL): rows 0..M-1, one weight.  Grouped: row tile i belongs to
  * expert tile_expert[i]; row r of the tile list is pair sorted_ids[r]; its A row is pair / gather_div (gather_div > 0,
- * scaled by row_scale[pair]) or r itself; its out row is the pair id (scatter) or r.  glu: w_e = [gate; up] of N rows each
- * and out (dtype) = clamped GLU; else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit).  With
- * tile_rows = 4 x b200_moe_tile_rows() the rows of A are the list b200_moe_gather_scale wrote (gather_div 0, no row_scale). */
+ * scaled by row_scale[pair] when given) or r itself; its out row is the pair id (scatter) or r.  glu: w_e = [gate; up] of N
+ * rows each and out (dtype) = the gated-linear unit with gate activation `act` (B200_ACT_*; `limit` for the clamped one);
+ * else out is fp32.  row_tiles = grid size (tiles beyond *num_tiles exit).  With tile_rows = 4 x b200_moe_tile_rows() the
+ * rows of A are the list b200_moe_gather_scale wrote (gather_div 0, no row_scale). */
 int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
                         int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
-                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, int tile_rows, void* stream);
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, int act, float limit, int tile_rows,
+                        void* stream);
+/* `batch` dense linears in one launch: out_b [M][N] = A_b [M][K] W_b [N][K]^T with A_b = a + b * a_batch_stride (pitch lda),
+ * W_b = w + b * w_batch_stride, out_b = out + b * out_batch_stride (pitch ldo); fp32 accumulation.  The result is
+ * multiplied by sigmoid(gate[row * gate_ld + b]) when gate != NULL and stored as fp32, or in `dtype` when out_typed. */
+int b200_batched_linear(const void* a, int lda, int64_t a_batch_stride, const void* w, int64_t w_batch_stride, void* out, int ldo,
+                        int64_t out_batch_stride, int batch, int M, int N, int K, int dtype, int out_typed, const float* gate,
+                        int gate_ld, void* stream);
+
+/* ---------------------------------------------------------------- post-norm hybrid decoders (delta rule + latent attention)
+ * x = table[token] * scale (+ bigram[row] when a bigram table is given: row = (prev * mul_prev + token * mul_cur) mod buckets,
+ * row `buckets` for a sequence's first token; the token before a portion is prev_state[slot], which is then set to the
+ * portion's last token).  out fp32 [T][W]; out_cast (or NULL): the same rows in table_dtype. */
+int b200_embed_bigram(const int32_t* tokens, const void* table, const void* bigram, int table_dtype, int buckets, int mul_prev,
+                      int mul_cur, int32_t* prev_state, const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot,
+                      const int32_t* seq_pos0, float* out, void* out_cast, int T, int W, int V, float scale, void* stream);
+/* s = sum_{c < nsum} y_weight[t * nsum + c] * y[t * nsum + c] (y_weight NULL: plain sum);
+ * x[t] += s / sqrt(mean(s^2) + eps) * (offset + w);  out_cast[t] = x[t] in out_dtype (when given). */
+int b200_rms_residual(float* x, const float* y, int nsum, const float* y_weight, const float* w, float offset, float eps,
+                      void* out_cast, int out_dtype, int T, int W, void* stream);
+/* out[t][0..n) = v / sqrt(mean(v^2) + eps) * (offset + w), v = columns [col0, col0 + n) of the fp32 rows `in` (pitch ld) */
+int b200_rmsnorm_cols(const float* in, int ld, int col0, int n, const float* w, float offset, float eps, void* out, int out_dtype,
+                      int ldo, int T, void* stream);
+/* o fp32 [T][H][P]: out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns gate_col0.. of fp32 rows (pitch ldg) */
+int b200_head_rmsnorm_gate(const float* o, const float* gate, int ldg, int gate_col0, const float* w, float eps, void* out,
+                           int out_dtype, int T, int H, int P, void* stream);
+/* gate_up fp32 [T][2 ff] (gate first): out = act(gate) * up, act = B200_ACT_SILU or B200_ACT_GELU_TANH */
+int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int act, void* stream);
+/* Gated delta rule, preparation: qkv fp32 rows [q: G*D | k: G*D | v: H*P] (pitch ldc) are the convolved activations; q and k
+ * become unit vectors per key head IN PLACE (x / sqrt(sum x^2 + unit_eps), q also times q_scale); beta_decay fp32 [T][2 H] =
+ * [sigmoid(raw_b) | exp(-exp(A_log) softplus(raw_a + dt_bias))] with raw_b / raw_a = columns b_col0 / a_col0 of the fp32
+ * rows proj; kq fp32 [T][G] = k . q. */
+int b200_delta_prep(float* qkv, int ldc, const float* proj, int ldp, int b_col0, int a_col0, const float* A_log,
+                    const float* dt_bias, float* beta_decay, float* kq, int T, int H, int G, int D, float q_scale, float unit_eps,
+                    void* stream);
+/* Gated delta rule over the prepared rows: per head  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+ * state fp32 [slots][H][P][D] (read when seq_pos0 > 0, zero otherwise, updated); out fp32 [T][H][P].  Head h reads key
+ * head h / (H / G).  D <= 1024. */
+int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const float* kq, float* state, const int32_t* seq_start,
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int G, int D, int P, void* stream);
+/* Latent attention, cache write: columns [col0, col0 + C) of the fp32 rows `in` are RMS-normed (weight norm_w) into
+ * pool[slot][0..C); the next R columns are the shared rotated key part: pairs (2i, 2i+1) of its first rot_n columns turn by
+ * the token's position with cos / sin from tables [positions][rot_n / 2], the rest is copied.  pool [slots][C + R]. */
+int b200_latent_kv_write(const float* in, int ld, int col0, int C, int R, int rot_n, const float* norm_w, float eps,
+                         const float* cos_table, const float* sin_table, const int32_t* tok_pos, const int64_t* slot_mapping,
+                         void* pool, int kv_dtype, int T, void* stream);
+/* Latent attention, query side: q fp32 rows [H][D + R] (pitch ldq).  q_nope [T][H * D] (nope_dtype) = the unrotated parts;
+ * q_att fp32 [T][H][C + R]: columns [C, C + R) = the rotated part, turned like the key's. */
+int b200_latent_q_prep(const float* q, int ldq, int H, int D, int R, int rot_n, int C, const float* cos_table,
+                       const float* sin_table, const int32_t* tok_pos, void* q_nope, int nope_dtype, float* q_att, int T,
+                       void* stream);
 
 #ifdef __cplusplus
 }

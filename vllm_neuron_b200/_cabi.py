@@ -12,8 +12,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200_paged.so")
 
 OK = 0
-ABI_VERSION = 9
+ABI_VERSION = 10
 BF16, FP8_E4M3, INT8, F32 = 0, 1, 2, 3
+ACT_SWISH_CLAMPED, ACT_SILU, ACT_GELU_TANH = 0, 1, 2   # gate activation of a gated-linear unit
+ROUTE_SIGMOID, ROUTE_SOFTMAX_TOP = 0, 1                # router weights: sigmoid of each chosen logit | softmax over the chosen
 
 _p = C.c_void_p
 _i = C.c_int
@@ -76,13 +78,24 @@ SIGNATURES = {
     "b200_causal_conv_silu": (_i, [_p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "b200_ssd_scan": (_i, [_p, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p, _p, _p, _p]),
     "b200_kv_write_vmix": (_i, [_p, _i, _i, _i, _p, _f, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
-    "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
-    "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _p]),
-    "b200_moe_topk": (_i, [_p, _i, _p, _p, _i, _i, _i, _p]),
+    "b200_swa_sink_attn": (_i, [_p, _i, _p, _p, _i, _p, _i64, _p, _p, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_swa_sink_attn_prefill": (_i, [_p, _i, _p, _p, _p, _i64, _p, _p, _p, _i, _i, _p, _f, _i, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "b200_moe_topk": (_i, [_p, _i, _p, _i, _p, _p, _i, _i, _i, _p]),
     "b200_moe_tile_rows": (_i, []),
     "b200_moe_gather_scale": (_i, [_p, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p]),
     "b200_moe_align": (_i, [_p, _i, _i, _p, _i, _p, _i, _p, _i, _p]),
-    "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _f, _i, _p]),
+    "b200_grouped_linear": (_i, [_p, _i, _p, _i, _p, _p, _i64, _p, _p, _i, _i, _i, _i, _i, _p, _i, _i, _i, _i, _f, _i, _p]),
+    "b200_batched_linear": (_i, [_p, _i, _i64, _p, _i64, _p, _i, _i64, _i, _i, _i, _i, _i, _i, _p, _i, _p]),
+    # post-norm hybrid decoders: bigram embedding, RMS-norm residual steps, gated delta rule, latent attention
+    "b200_embed_bigram": (_i, [_p, _p, _p, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _f, _p]),
+    "b200_rms_residual": (_i, [_p, _p, _i, _p, _p, _f, _f, _p, _i, _i, _i, _p]),
+    "b200_rmsnorm_cols": (_i, [_p, _i, _i, _i, _p, _f, _f, _p, _i, _i, _i, _p]),
+    "b200_head_rmsnorm_gate": (_i, [_p, _p, _i, _i, _p, _f, _p, _i, _i, _i, _i, _p]),
+    "b200_glu": (_i, [_p, _p, _i, _i, _i, _i, _p]),
+    "b200_delta_prep": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p]),
+    "b200_delta_scan": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_latent_kv_write": (_i, [_p, _i, _i, _i, _i, _i, _p, _f, _p, _p, _p, _p, _p, _i, _i, _p]),
+    "b200_latent_q_prep": (_i, [_p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p, _i, _p]),
 }
 
 _lib = None

@@ -12,7 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200_paged.so")
 SOURCES = ["host.cu", "kv_ops.cu", "paged_attn.cu", "paged_attn_prefill_tc.cu", "gemm_tcgen05.cu", "tp_allreduce.cu", "sampling.cu",
-           "dyt_norm.cu", "ssm_scan.cu", "swa_attn.cu", "swa_attn_prefill.cu", "moe.cu"]
+           "dyt_norm.cu", "ssm_scan.cu", "swa_attn.cu", "swa_attn_prefill.cu", "moe.cu", "rms_norm.cu", "delta_rule.cu",
+           "latent_attn.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "hybrid_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "b200_paged.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,13 +44,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    newest_header = max(os.path.getmtime(h) for h in HEADERS)
     for s in SOURCES:
         o = os.path.join(HERE, "build", s.replace(".cu", ".o"))
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, s), "-o", o]
+        objs.append(o)
+        src = os.path.join(CSRC, s)
+        if not force and os.path.exists(o) and os.path.getmtime(o) > max(os.path.getmtime(src), newest_header):
+            continue  # this object is up to date: only changed sources are recompiled
+        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", o]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-        objs.append(o)
     for s, p in procs:
         out, _ = p.communicate()
         if verbose or p.returncode:

@@ -1,0 +1,236 @@
+// Gated delta-rule recurrence over a ragged batch, beside the selective state-space scan (ssm_scan.cu).
+// Per head, token by token, with a matrix state S [D keys x P values] in fp32:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q          (o sees the token's own write)
+//   * delta_prep: per token, q and k (after their short convolution) become unit vectors per key head,
+//     x / sqrt(sum x^2 + unit_eps), q also times q_scale; beta = sigmoid(raw_b), g = exp(-exp(A_log) softplus(raw_a + dt_bias));
+//     k . q per key head is kept for the read-out.  Everything fp32.
+//   * delta_scan: the columns of S evolve independently (column j only needs v_j), so a CTA owns PC columns of one head of
+//     one sequence and L lanes share a column, each keeping R consecutive rows in registers.  With s_k = S^T k and
+//     s_q = S^T q taken BEFORE the update (one pass over the registers, one shuffle tree for both),
+//         u = beta (v - g s_k),   S <- g S + k u,   o = g s_q + u (k . q)
+//     is the recurrence above, term for term.  Tokens are staged through shared memory in chunks, the next chunk's
+//     cp.async copies in flight under the current chunk's steps.  State layout [slots][H][P][D] (a column's rows are
+//     contiguous), read when the sequence continues (pos0 > 0), zero otherwise, written back at the end of the portion.
+#include <math.h>
+
+#include "hybrid_common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// one CTA per token: warps take the key heads (unit norms, k . q), threads the value heads (beta, decay)
+__global__ void delta_prep_kernel(float* __restrict__ qkv, int ldc, const float* __restrict__ proj, int ldp, int b_col0, int a_col0,
+                                  const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ bg,
+                                  float* __restrict__ kq, int H, int G, int D, float q_scale, float unit_eps) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < G; g += nw) {
+    float* q = qkv + (int64_t)t * ldc + (int64_t)g * D;
+    float* k = q + (int64_t)G * D;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      sq += q[i] * q[i];
+      sk += k[i] * k[i];
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float iq = q_scale / sqrtf(sq + unit_eps), ik = 1.0f / sqrtf(sk + unit_eps);
+    float dot = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float a = q[i] * iq, b = k[i] * ik;
+      q[i] = a;
+      k[i] = b;
+      dot += a * b;
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) kq[(int64_t)t * G + g] = dot;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float rb = proj[(int64_t)t * ldp + b_col0 + h], ra = proj[(int64_t)t * ldp + a_col0 + h];
+    bg[(int64_t)t * 2 * H + h] = 1.0f / (1.0f + expf(-rb));
+    bg[(int64_t)t * 2 * H + H + h] = expf(-expf(A_log[h]) * softplus_f(ra + dt_bias[h]));
+  }
+}
+
+constexpr int DS_THREADS = 128;
+constexpr int DS_CHUNK = 16;  // tokens staged per shared-memory buffer
+
+template <int N>
+__device__ __forceinline__ void cp_async_f32(uint32_t dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(src), "n"(N * 4) : "memory");
+}
+
+// grid (P / PC column chunks, H, sequences); thread = (column cl = tid / L, lane part l = tid % L), rows [l R, l R + R)
+template <int R>
+__global__ void __launch_bounds__(DS_THREADS)
+    delta_scan_kernel(const float* __restrict__ qkv, int ldc, const float* __restrict__ bg, const float* __restrict__ kq,
+                      float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
+                      const int32_t* __restrict__ seq_pos0, float* __restrict__ out, int H, int G, int D, int P, int L, int vec4) {
+  griddep_launch();
+  griddep_wait();
+  const int sq = blockIdx.z, h = blockIdx.y, PC = DS_THREADS / L, c0 = blockIdx.x * PC;
+  const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
+  if (n <= 0) return;
+  const int g = h / (H / G);
+  const int Dp = L * R;  // padded key length: rows past D stay zero
+  extern __shared__ __align__(16) float ds_sm[];
+  // per stage: q [CH][Dp] | k [CH][Dp] | v [CH][PC] | beta, decay, k.q [3][CH]
+  const int stage_f = DS_CHUNK * (2 * Dp + PC + 3);
+  float* o_s = ds_sm + 2 * stage_f;  // [CH][PC]
+  const int tid = threadIdx.x, cl = tid / L, l = tid - cl * L;
+  const int col = c0 + cl;
+  const bool col_ok = col < P;
+  for (int i = tid; i < 2 * stage_f; i += DS_THREADS) ds_sm[i] = 0.f;  // the pads (rows past D, columns past P) stay zero
+  __syncthreads();
+  const uint32_t sm0 = smem_u32(ds_sm);
+  const int vcols = P - c0 < PC ? P - c0 : PC;
+  auto issue = [&](int ck) {
+    const int i0 = ck * DS_CHUNK;
+    const int cnt = n - i0 < DS_CHUNK ? n - i0 : DS_CHUNK;
+    if (cnt > 0) {
+      const uint32_t base = sm0 + (uint32_t)((ck & 1) * stage_f * 4);
+      const float* src_q = qkv + (int64_t)(t0 + i0) * ldc + (int64_t)g * D;
+      const float* src_k = src_q + (int64_t)G * D;
+      const float* src_v = qkv + (int64_t)(t0 + i0) * ldc + 2 * (int64_t)G * D + (int64_t)h * P + c0;
+      if (vec4) {
+        const int dq = D >> 2, vq = vcols >> 2;
+        for (int i = tid; i < cnt * dq; i += DS_THREADS) {
+          const int r = i / dq, d = (i - r * dq) * 4;
+          cp_async_f32<4>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
+          cp_async_f32<4>(base + (uint32_t)(((DS_CHUNK + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
+        }
+        for (int i = tid; i < cnt * vq; i += DS_THREADS) {
+          const int r = i / vq, d = (i - r * vq) * 4;
+          cp_async_f32<4>(base + (uint32_t)((2 * DS_CHUNK * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+        }
+      } else {
+        for (int i = tid; i < cnt * D; i += DS_THREADS) {
+          const int r = i / D, d = i - r * D;
+          cp_async_f32<1>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
+          cp_async_f32<1>(base + (uint32_t)(((DS_CHUNK + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
+        }
+        for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
+          const int r = i / vcols, d = i - r * vcols;
+          cp_async_f32<1>(base + (uint32_t)((2 * DS_CHUNK * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+        }
+      }
+      const uint32_t sc = base + (uint32_t)((DS_CHUNK * (2 * Dp + PC)) * 4);
+      for (int i = tid; i < cnt; i += DS_THREADS) {
+        cp_async_f32<1>(sc + (uint32_t)(i * 4), bg + (int64_t)(t0 + i0 + i) * 2 * H + h);
+        cp_async_f32<1>(sc + (uint32_t)((DS_CHUNK + i) * 4), bg + (int64_t)(t0 + i0 + i) * 2 * H + H + h);
+        cp_async_f32<1>(sc + (uint32_t)((2 * DS_CHUNK + i) * 4), kq + (int64_t)(t0 + i0 + i) * G + g);
+      }
+    }
+    cp_async_commit();  // an empty group past the end keeps the wait counts uniform
+  };
+  // ---- state
+  float S[R];
+  float* srow = state + (((int64_t)seq_slot[sq] * H + h) * P + (col_ok ? col : 0)) * D + l * R;
+#pragma unroll
+  for (int r = 0; r < R; ++r) S[r] = 0.f;
+  if (seq_pos0[sq] > 0 && col_ok) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (l * R + r < D) S[r] = srow[r];
+  }
+  const int chunks = (n + DS_CHUNK - 1) / DS_CHUNK;
+  issue(0);
+  for (int ck = 0; ck < chunks; ++ck) {
+    issue(ck + 1);
+    cp_async_wait<1>();
+    __syncthreads();  // chunk ck of every thread has landed; o_s of chunk ck - 1 has been flushed
+    const float* st = ds_sm + (ck & 1) * stage_f;
+    const float* qs = st + l * R;
+    const float* ks = st + DS_CHUNK * Dp + l * R;
+    const float* vs = st + 2 * DS_CHUNK * Dp + cl;
+    const float* sc = st + DS_CHUNK * (2 * Dp + PC);
+    const int cnt = n - ck * DS_CHUNK < DS_CHUNK ? n - ck * DS_CHUNK : DS_CHUNK;
+    for (int c = 0; c < cnt; ++c) {
+      float kr[R];
+      float pk0 = 0.f, pk1 = 0.f, pq0 = 0.f, pq1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + c * Dp + r);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + c * Dp + r);
+        kr[r] = k4.x, kr[r + 1] = k4.y, kr[r + 2] = k4.z, kr[r + 3] = k4.w;
+        pk0 += S[r] * k4.x + S[r + 2] * k4.z;
+        pk1 += S[r + 1] * k4.y + S[r + 3] * k4.w;
+        pq0 += S[r] * q4.x + S[r + 2] * q4.z;
+        pq1 += S[r + 1] * q4.y + S[r + 3] * q4.w;
+      }
+      float pk = pk0 + pk1, pq = pq0 + pq1;
+      for (int o = L >> 1; o > 0; o >>= 1) {
+        pk += __shfl_xor_sync(0xffffffffu, pk, o);
+        pq += __shfl_xor_sync(0xffffffffu, pq, o);
+      }
+      const float beta = sc[c], gd = sc[DS_CHUNK + c], dkq = sc[2 * DS_CHUNK + c];
+      const float u = beta * (vs[c * PC] - gd * pk);
+#pragma unroll
+      for (int r = 0; r < R; ++r) S[r] = gd * S[r] + kr[r] * u;
+      if (l == 0) o_s[c * PC + cl] = gd * pq + u * dkq;
+    }
+    __syncthreads();  // o_s complete; everyone is done with stage ck & 1 before chunk ck + 2 is copied into it
+    for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
+      const int r = i / vcols, d = i - r * vcols;
+      out[((int64_t)(t0 + ck * DS_CHUNK + r) * H + h) * P + c0 + d] = o_s[r * PC + d];
+    }
+  }
+  cp_async_wait<0>();
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (l * R + r < D) srow[r] = S[r];
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_delta_prep(float* qkv, int ldc, const float* proj, int ldp, int b_col0, int a_col0, const float* A_log,
+                    const float* dt_bias, float* beta_decay, float* kq, int T, int H, int G, int D, float q_scale, float unit_eps,
+                    void* stream) {
+  B200_REQUIRE(qkv && proj && A_log && dt_bias && beta_decay && kq, "delta_prep: null pointer");
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && D > 0, "delta_prep: %d heads over %d key heads of %d", H, G, D);
+  if (T <= 0) return B200_OK;
+  B200_CUDA_OK(launch_kernel(delta_prep_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, qkv, ldc, proj, ldp, b_col0, a_col0,
+                             A_log, dt_bias, beta_decay, kq, H, G, D, q_scale, unit_eps));
+  return B200_OK;
+}
+
+int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const float* kq, float* state, const int32_t* seq_start,
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int G, int D, int P, void* stream) {
+  B200_REQUIRE(qkv && beta_decay && kq && state && seq_start && seq_slot && seq_pos0 && out, "delta_scan: null pointer");
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "delta_scan: %d heads over %d key heads", H, G);
+  B200_REQUIRE(D >= 1 && D <= 1024 && P >= 1, "delta_scan: key size %d (1..1024 supported)", D);
+  if (B <= 0) return B200_OK;
+  // L lanes per column (a power of two), R rows per lane: eight rows while D <= 256
+  int L = 1;
+  while (L < 32 && L * 8 < D) L <<= 1;
+  const int need = (D + L - 1) / L;
+  const int R = need <= 8 ? 8 : need <= 16 ? 16 : 32;
+  const int PC = DS_THREADS / L;
+  const int vcols_min = P % PC ? P % PC : PC;
+  const int vec4 = D % 4 == 0 && ldc % 4 == 0 && P % 4 == 0 && PC % 4 == 0 && vcols_min % 4 == 0 && !((uintptr_t)qkv & 15);
+  const size_t smem = (size_t)(2 * DS_CHUNK * (2 * L * R + PC + 3) + DS_CHUNK * PC) * 4;
+  dim3 grid((P + PC - 1) / PC, H, B);
+  cudaStream_t st = (cudaStream_t)stream;
+#define DS_LAUNCH(RR)                                                                                                        \
+  do {                                                                                                                       \
+    if (smem > 48 * 1024)                                                                                                    \
+      B200_CUDA_OK(cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+    B200_CUDA_OK(launch_kernel(delta_scan_kernel<RR>, grid, dim3(DS_THREADS), smem, st, qkv, ldc, beta_decay, kq, state,     \
+                               seq_start, seq_slot, seq_pos0, out, H, G, D, P, L, vec4));                                   \
+  } while (0)
+  if (R == 8) DS_LAUNCH(8);
+  else if (R == 16) DS_LAUNCH(16);
+  else DS_LAUNCH(32);
+#undef DS_LAUNCH
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -1,6 +1,7 @@
 // Mixture-of-experts feed-forward over a token batch, and the generic grouped / dense linear kernel it is built on.
-//   * moe_topk: over the fp32 router logits (a linear of the layer's input): score = sigmoid(logit); the `top` largest are
-//     chosen (ties go to the lower expert index) and the chosen SCORES are the routing weights (no renormalisation);
+//   * moe_topk: over the fp32 router logits (a linear of the layer's input, plus an optional per-expert bias): the `top`
+//     largest are chosen (ties go to the lower expert index); the routing weights are either the sigmoid of each chosen
+//     logit (no renormalisation) or the softmax over the chosen logits only;
 //   * moe_align: counting sort of the (token, choice) pairs by expert into row tiles of MOE_BM, each tile owned by one
 //     expert (ragged tails padded with -1), so the expert GEMMs run as one launch without the host knowing the counts;
 //   * grouped_linear: out = A W_e^T with fp32 accumulation over K in ascending order (the result of a row does not depend
@@ -19,29 +20,39 @@ constexpr int GL_BN = 64;
 constexpr int GL_BK = 16;
 constexpr int GL_THREADS = 256;
 
-// one thread per token: the `top` largest logits (ties to the lower index); weight = sigmoid(logit)
-__global__ void moe_topk_kernel(const float* __restrict__ z, int ld, int E, int top, int32_t* __restrict__ idx,
-                                float* __restrict__ wt, int ntok) {
+// one thread per token: the `top` largest logits (+ bias; ties to the lower index); weight = sigmoid(logit), or the softmax
+// over the chosen logits (mode B200_ROUTE_SOFTMAX_TOP)
+__global__ void moe_topk_kernel(const float* __restrict__ z, int ld, const float* __restrict__ bias, int mode, int E, int top,
+                                int32_t* __restrict__ idx, float* __restrict__ wt, int ntok) {
   griddep_launch();
   griddep_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= ntok) return;
   const float* zr = z + (int64_t)t * ld;
   int32_t* out = idx + (int64_t)t * top;
+  float* w = wt + (int64_t)t * top;
   for (int c = 0; c < top; ++c) {
     float best = -INFINITY;
     int bi = -1;
     for (int e = 0; e < E; ++e) {
       bool taken = false;
       for (int k = 0; k < c; ++k) taken |= out[k] == e;
-      const float v = zr[e];
+      const float v = zr[e] + (bias ? bias[e] : 0.f);
       if (!taken && (bi < 0 || v > best)) {
         best = v;
         bi = e;
       }
     }
     out[c] = bi;
-    wt[(int64_t)t * top + c] = 1.0f / (1.0f + expf(-best));
+    w[c] = best;
+  }
+  if (mode == B200_ROUTE_SOFTMAX_TOP) {
+    const float m = w[0];  // the first chosen is the largest
+    float sum = 0.f;
+    for (int c = 0; c < top; ++c) sum += expf(w[c] - m);
+    for (int c = 0; c < top; ++c) w[c] = expf(w[c] - m) / sum;
+  } else {
+    for (int c = 0; c < top; ++c) w[c] = 1.0f / (1.0f + expf(-w[c]));
   }
 }
 
@@ -78,13 +89,24 @@ __global__ void moe_align_kernel(const int32_t* __restrict__ idx, int npairs, in
 
 enum { GL_EPI_STORE = 0, GL_EPI_GLU = 1 };
 
+// gated-linear unit on fp32 accumulators: clamped swish (a = min(g, L), b = clip(u, -L, L): (b + 1) a sigmoid(1.702 a)),
+// SiLU(g) u, or tanh-GELU(g) u
+__device__ __forceinline__ float glu_act(float g, float u, int act, float limit) {
+  if (act == B200_ACT_SILU) return g / (1.0f + expf(-g)) * u;
+  if (act == B200_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 // Row tile `blockIdx.x` (MOE_BM rows), column tile `blockIdx.y` (GL_BN outputs).  256 threads, each 2 rows x 4 columns.
 template <typename T, int EPI>
 __global__ void __launch_bounds__(GL_THREADS)
     grouped_linear_kernel(const T* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
                           const float* __restrict__ row_scale, const T* __restrict__ w, int64_t w_stride,
                           const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles, int M, int N, int K,
-                          void* __restrict__ out, int ldo, int scatter, float limit) {
+                          void* __restrict__ out, int ldo, int scatter, float limit, int act, int64_t a_zs, int64_t o_zs,
+                          int store_typed, const float* __restrict__ gate, int gate_ld) {
   griddep_launch();
   griddep_wait();
   constexpr int NW = EPI == GL_EPI_GLU ? 2 : 1;
@@ -95,8 +117,9 @@ __global__ void __launch_bounds__(GL_THREADS)
   __shared__ float rsc[MOE_BM];
   const int tile = blockIdx.x;
   if (num_tiles && tile >= *num_tiles) return;
-  const int e = tile_expert ? tile_expert[tile] : 0;
+  const int e = tile_expert ? tile_expert[tile] : blockIdx.z;  // z-batched dense launches: one weight per batch index
   const T* we = w + (int64_t)e * w_stride;
+  a += (int64_t)blockIdx.z * a_zs;
   const int n0 = blockIdx.y * GL_BN;
   if (threadIdx.x < MOE_BM) {
     const int r = tile * MOE_BM + threadIdx.x;
@@ -162,12 +185,14 @@ __global__ void __launch_bounds__(GL_THREADS)
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + 4 * tx + j;
       if (n >= N) continue;
+      const int64_t o = (int64_t)blockIdx.z * o_zs + (int64_t)dst * ldo + n;
       if (EPI == GL_EPI_GLU) {
-        const float g = fminf(acc[0][i][j], limit);
-        const float u = fminf(fmaxf(acc[NW - 1][i][j], -limit), limit);
-        stf((T*)out, (int64_t)dst * ldo + n, g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+        stf((T*)out, o, glu_act(acc[0][i][j], acc[NW - 1][i][j], act, limit));
       } else {
-        ((float*)out)[(int64_t)dst * ldo + n] = acc[0][i][j];
+        float v = acc[0][i][j];
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[(int64_t)dst * gate_ld + blockIdx.z]));
+        if (store_typed) stf((T*)out, o, v);
+        else ((float*)out)[o] = v;
       }
     }
   }
@@ -187,7 +212,8 @@ __global__ void __launch_bounds__(128)
     grouped_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids, int gather_div,
                        const float* __restrict__ row_scale, const __nv_bfloat16* __restrict__ w, int64_t w_stride,
                        const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ num_tiles, int M, int N, int K,
-                       void* __restrict__ out, int ldo, int scatter, float limit) {
+                       void* __restrict__ out, int ldo, int scatter, float limit, int act, int64_t a_zs, int64_t o_zs,
+                       int store_typed, const float* __restrict__ gate, int gate_ld) {
   griddep_launch();
   griddep_wait();
   constexpr int R = 1;            // 32-row sub-tiles per CTA (prompt-sized batches take grouped_mma_pipe_kernel instead)
@@ -199,8 +225,9 @@ __global__ void __launch_bounds__(128)
   __shared__ float rsc[BM];
   const int tile = blockIdx.x;
   if (num_tiles && tile >= *num_tiles) return;
-  const int e = tile_expert ? tile_expert[tile] : 0;
+  const int e = tile_expert ? tile_expert[tile] : blockIdx.z;  // z-batched dense launches: one weight per batch index
   const __nv_bfloat16* we = w + (int64_t)e * w_stride;
+  a += (int64_t)blockIdx.z * a_zs;
   constexpr int BN = EPI == GL_EPI_GLU ? 64 : 128;  // outputs per CTA
   const int n0 = blockIdx.y * BN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -319,15 +346,18 @@ __global__ void __launch_bounds__(128)
         for (int j = 0; j < 2; ++j) {
           const int n = n0 + 16 * warp + 8 * j + col;
           if (n >= N) continue;
-          const float g = fminf(acc[mt][j][c], limit);
-          const float u = fminf(fmaxf(acc[mt][j + 2][c], -limit), limit);
-          ((__nv_bfloat16*)out)[(int64_t)dst * ldo + n] = __float2bfloat16_rn(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+          ((__nv_bfloat16*)out)[(int64_t)blockIdx.z * o_zs + (int64_t)dst * ldo + n] =
+              __float2bfloat16_rn(glu_act(acc[mt][j][c], acc[mt][j + 2][c], act, limit));
         }
       } else {
+        const float gt = gate ? 1.0f / (1.0f + expf(-gate[(int64_t)dst * gate_ld + blockIdx.z])) : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int n = n0 + 32 * warp + 8 * j + col;
-          if (n < N) ((float*)out)[(int64_t)dst * ldo + n] = acc[mt][j][c];
+          if (n >= N) continue;
+          const int64_t o = (int64_t)blockIdx.z * o_zs + (int64_t)dst * ldo + n;
+          if (store_typed) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(acc[mt][j][c] * gt);
+          else ((float*)out)[o] = acc[mt][j][c] * gt;
         }
       }
     }
@@ -346,17 +376,19 @@ __global__ void moe_gather_scale_kernel(const __nv_bfloat16* __restrict__ h, int
   const int r = blockIdx.x;
   if (r >= *num_tiles * tile_rows) return;
   const int id = sorted_ids[r];
-  const float sc = id >= 0 ? weight[id] : 0.f;
+  const float sc = id >= 0 ? (weight ? weight[id] : 1.0f) : 0.f;
   const __nv_bfloat16* src = h + (int64_t)(id >= 0 ? id / top : 0) * ldh;
   for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {
     uint4 v = make_uint4(0, 0, 0, 0);
     if (id >= 0) {
       v = *reinterpret_cast<const uint4*>(src + c);
-      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+      if (sc != 1.0f) {
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(h2[i]);
-        h2[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          h2[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
       }
     }
     *reinterpret_cast<uint4*>(out + (int64_t)r * W + c) = v;
@@ -376,7 +408,7 @@ __global__ void __launch_bounds__(GP_THREADS)
     grouped_mma_pipe_kernel(const __nv_bfloat16* __restrict__ a, int lda, const int32_t* __restrict__ sorted_ids,
                             const __nv_bfloat16* __restrict__ w, int64_t w_stride, const int32_t* __restrict__ tile_expert,
                             const int32_t* __restrict__ num_tiles, int N, int K, void* __restrict__ out, int ldo, int scatter,
-                            float limit) {
+                            float limit, int act) {
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) unsigned char gp_smem[];
@@ -483,9 +515,7 @@ __global__ void __launch_bounds__(GP_THREADS)
         for (int j = 0; j < 2; ++j) {
           const int n = n0 + 16 * wn + 8 * j + col;
           if (n >= N) continue;
-          const float g = fminf(acc[mt][j][c], limit);
-          const float u = fminf(fmaxf(acc[mt][j + 2][c], -limit), limit);
-          ((__nv_bfloat16*)out)[(int64_t)dstrow * ldo + n] = __float2bfloat16_rn(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+          ((__nv_bfloat16*)out)[(int64_t)dstrow * ldo + n] = __float2bfloat16_rn(glu_act(acc[mt][j][c], acc[mt][j + 2][c], act, limit));
         }
       } else {
 #pragma unroll
@@ -503,12 +533,14 @@ using namespace b200;
 
 extern "C" {
 
-int b200_moe_topk(const float* logits, int ld, int32_t* topk_idx, float* topk_weight, int T, int E, int top, void* stream) {
+int b200_moe_topk(const float* logits, int ld, const float* bias, int mode, int32_t* topk_idx, float* topk_weight, int T, int E,
+                  int top, void* stream) {
   B200_REQUIRE(logits && topk_idx && topk_weight, "moe_topk: null pointer");
   B200_REQUIRE(E >= 1 && top >= 1 && top <= E && ld >= E, "moe_topk: top %d of %d experts", top, E);
+  B200_REQUIRE(mode == B200_ROUTE_SIGMOID || mode == B200_ROUTE_SOFTMAX_TOP, "moe_topk: routing mode %d", mode);
   if (T <= 0) return B200_OK;
-  B200_CUDA_OK(launch_kernel(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, logits, ld, E, top,
-                             topk_idx, topk_weight, T));
+  B200_CUDA_OK(launch_kernel(moe_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, logits, ld, bias, mode, E,
+                             top, topk_idx, topk_weight, T));
   return B200_OK;
 }
 
@@ -516,7 +548,7 @@ int b200_moe_tile_rows(void) { return MOE_BM; }
 
 int b200_moe_gather_scale(const void* h, int ldh, const int32_t* sorted_ids, int cap, int top, const float* weight,
                           const int32_t* num_tiles, int tile_rows, void* out, int W, void* stream) {
-  B200_REQUIRE(h && sorted_ids && weight && num_tiles && out, "moe_gather_scale: null pointer");
+  B200_REQUIRE(h && sorted_ids && num_tiles && out, "moe_gather_scale: null pointer");
   B200_REQUIRE(top >= 1 && W % 8 == 0 && ldh % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)out & 15),
                "moe_gather_scale: rows of %d bf16 elements (pitch %d) are not 16-byte vectors", W, ldh);
   if (cap <= 0) return B200_OK;
@@ -540,22 +572,26 @@ int b200_moe_align(const int32_t* topk_idx, int npairs, int E, int32_t* sorted_i
 
 int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int gather_div, const float* row_scale, const void* w,
                         int64_t w_expert_stride, const int32_t* tile_expert, const int32_t* num_tiles, int row_tiles, int M, int N,
-                        int K, int dtype, void* out, int ldo, int scatter, int glu, float limit, int tile_rows, void* stream) {
+                        int K, int dtype, void* out, int ldo, int scatter, int glu, int act, float limit, int tile_rows,
+                        void* stream) {
   B200_REQUIRE(a && w && out, "grouped_linear: null pointer");
   B200_REQUIRE(N > 0 && K > 0 && row_tiles >= 0, "grouped_linear: bad shape N=%d K=%d", N, K);
   B200_REQUIRE(sorted_ids || (!tile_expert && !num_tiles && !row_scale), "grouped_linear: expert tiles need the sorted pair list");
+  B200_REQUIRE(!glu || act == B200_ACT_SWISH_CLAMPED || act == B200_ACT_SILU || act == B200_ACT_GELU_TANH,
+               "grouped_linear: activation %d", act);
   if (row_tiles == 0) return B200_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const bool mma_ok = dtype == B200_BF16 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 && !((uintptr_t)a & 15) &&
                       !((uintptr_t)w & 15);
   B200_REQUIRE(tile_rows == MOE_BM || (tile_rows == MOE_BM * MOE_WIDE && mma_ok),
                "grouped_linear: %d rows per tile (32, or 128 for 16-byte aligned bf16 operands)", tile_rows);
+  const float* no_gate = nullptr;
   if (mma_ok) {
     using BT = __nv_bfloat16;
 #define GM_LAUNCH(EPI, BN)                                                                                                   \
   B200_CUDA_OK(launch_kernel(grouped_mma_kernel<EPI>, dim3(row_tiles, (N + BN - 1) / BN), dim3(128), 0, st, (const BT*)a, lda, \
                              sorted_ids, gather_div, row_scale, (const BT*)w, w_expert_stride, tile_expert, num_tiles, M, N, K, \
-                             out, ldo, scatter, limit))
+                             out, ldo, scatter, limit, act, (int64_t)0, (int64_t)0, 0, no_gate, 0))
     if (tile_rows == MOE_BM) {
       if (glu) GM_LAUNCH(GL_EPI_GLU, 64);
       else GM_LAUNCH(GL_EPI_STORE, 128);
@@ -569,7 +605,7 @@ int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int g
     B200_CUDA_OK(cudaFuncSetAttribute(grouped_mma_pipe_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));  \
     B200_CUDA_OK(launch_kernel(grouped_mma_pipe_kernel<EPI>, dim3(row_tiles, (N + BN - 1) / BN), dim3(GP_THREADS), smem, st,   \
                                (const BT*)a, lda, sorted_ids, (const BT*)w, w_expert_stride, tile_expert, num_tiles, N, K, out, \
-                               ldo, scatter, limit));                                                                          \
+                               ldo, scatter, limit, act));                                                                     \
   } while (0)
       if (glu) GP_LAUNCH(GL_EPI_GLU, 64);
       else GP_LAUNCH(GL_EPI_STORE, 128);
@@ -583,12 +619,39 @@ int b200_grouped_linear(const void* a, int lda, const int32_t* sorted_ids, int g
     if (glu)
       B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_GLU>, grid, dim3(GL_THREADS), 0, st, (const ET*)a, lda, sorted_ids,
                                  gather_div, row_scale, (const ET*)w, w_expert_stride, tile_expert, num_tiles, M, N, K, out, ldo,
-                                 scatter, limit));
+                                 scatter, limit, act, (int64_t)0, (int64_t)0, 0, no_gate, 0));
     else
       B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_STORE>, grid, dim3(GL_THREADS), 0, st, (const ET*)a, lda,
                                  sorted_ids, gather_div, row_scale, (const ET*)w, w_expert_stride, tile_expert, num_tiles, M, N, K,
-                                 out, ldo, scatter, limit));
+                                 out, ldo, scatter, limit, act, (int64_t)0, (int64_t)0, 0, no_gate, 0));
   });
+  return B200_OK;
+}
+
+int b200_batched_linear(const void* a, int lda, int64_t a_batch_stride, const void* w, int64_t w_batch_stride, void* out, int ldo,
+                        int64_t out_batch_stride, int batch, int M, int N, int K, int dtype, int out_typed, const float* gate,
+                        int gate_ld, void* stream) {
+  B200_REQUIRE(a && w && out, "batched_linear: null pointer");
+  B200_REQUIRE(N > 0 && K > 0 && batch >= 1 && batch <= 65535, "batched_linear: bad shape N=%d K=%d batch=%d", N, K, batch);
+  if (M <= 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int row_tiles = (M + MOE_BM - 1) / MOE_BM;
+  const int32_t* none = nullptr;
+  const float* no_scale = nullptr;
+  const bool mma_ok = dtype == B200_BF16 && K % 8 == 0 && lda % 8 == 0 && a_batch_stride % 8 == 0 && w_batch_stride % 8 == 0 &&
+                      !((uintptr_t)a & 15) && !((uintptr_t)w & 15);
+  if (mma_ok) {
+    using BT = __nv_bfloat16;
+    B200_CUDA_OK(launch_kernel(grouped_mma_kernel<GL_EPI_STORE>, dim3(row_tiles, (N + 127) / 128, batch), dim3(128), 0, st,
+                               (const BT*)a, lda, none, 0, no_scale, (const BT*)w, w_batch_stride, none, none, M, N, K, out, ldo, 0,
+                               0.f, 0, a_batch_stride, out_batch_stride, out_typed, gate, gate_ld));
+    return B200_OK;
+  }
+  dim3 grid(row_tiles, (N + GL_BN - 1) / GL_BN, batch);
+  B200_DISPATCH_ELEM(dtype, ET,
+                     B200_CUDA_OK(launch_kernel(grouped_linear_kernel<ET, GL_EPI_STORE>, grid, dim3(GL_THREADS), 0, st, (const ET*)a,
+                                                lda, none, 0, no_scale, (const ET*)w, w_batch_stride, none, none, M, N, K, out, ldo, 0,
+                                                0.f, 0, a_batch_stride, out_batch_stride, out_typed, gate, gate_ld)));
   return B200_OK;
 }
 

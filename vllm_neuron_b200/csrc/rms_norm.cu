@@ -1,0 +1,217 @@
+// Per-row kernels of hybrid decoders with post-norm residual branches (x += N(branch(x)), N an RMS norm whose weight may
+// be stored around zero): token + hashed-bigram embedding, the fused "residual += norm(weighted sum of branch rows);
+// next operand = cast(residual)" step, an RMS norm over a column range, the per-head RMS norm with an output gate that
+// closes a recurrent mixer, and gated-linear-unit activations.  The residual stream and all norm arithmetic are fp32;
+// outputs that feed a GEMM are written in the GEMM operand type.
+#include "hybrid_common.cuh"
+
+namespace b200 {
+
+// sum over the CTA (every thread gets it); `red` holds 33 floats
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float s = threadIdx.x < ((blockDim.x + 31) >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) red[32] = s;
+  }
+  __syncthreads();
+  const float out = red[32];
+  __syncthreads();  // `red` may be reused right away
+  return out;
+}
+
+// x[t] = table[token] * scale + bigram[row];  row = (prev * mul_prev + token * mul_cur) mod buckets, and row `buckets`
+// (the table's last) for a sequence's first token.  The token before a portion comes from prev_state[slot]; the CTA of
+// a portion's first token reads it and then stores the portion's last token there.
+template <typename WT, typename OT>
+__global__ void embed_bigram_kernel(const int32_t* __restrict__ tokens, const WT* __restrict__ table, const WT* __restrict__ bigram,
+                                    int buckets, int mul_prev, int mul_cur, int32_t* __restrict__ prev_state,
+                                    const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_start,
+                                    const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_pos0,
+                                    float* __restrict__ out, OT* __restrict__ out_cast, int W, int V, float scale) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  int64_t brow = -1;
+  if (bigram) {
+    const int s = tok_seq[t];
+    const int t0 = seq_start[s];
+    if (t > t0) {
+      int prev = tokens[t - 1];
+      prev = prev < 0 ? 0 : (prev >= V ? V - 1 : prev);
+      brow = ((int64_t)prev * mul_prev + (int64_t)tok * mul_cur) % buckets;
+    } else {
+      const int slot = seq_slot[s];
+      brow = seq_pos0[s] > 0 ? ((int64_t)prev_state[slot] * mul_prev + (int64_t)tok * mul_cur) % buckets : buckets;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int last = tokens[seq_start[s + 1] - 1];
+        prev_state[slot] = last < 0 ? 0 : (last >= V ? V - 1 : last);
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = ldf(table, (int64_t)tok * W + i) * scale;
+    if (brow >= 0) v += ldf(bigram, brow * W + i);
+    out[(int64_t)t * W + i] = v;
+    if (out_cast) stf(out_cast, (int64_t)t * W + i, v);
+  }
+}
+
+// s = sum_{c < nsum} wt[t * nsum + c] * y[(t * nsum + c)] (wt NULL: plain sum);  x[t] += s / sqrt(mean(s^2) + eps) * (offset + w);
+// out_cast[t] = x[t] in the operand type (when given).  One CTA per token; the row is held in shared memory.
+template <typename OT>
+__global__ void rms_residual_kernel(float* __restrict__ x, const float* __restrict__ y, int nsum, const float* __restrict__ wt,
+                                    const float* __restrict__ w, float offset, float eps, OT* __restrict__ out_cast, int W) {
+  griddep_launch();
+  griddep_wait();
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float s = 0.f;
+    for (int c = 0; c < nsum; ++c) {
+      const float v = y[((int64_t)t * nsum + c) * W + i];
+      s += wt ? wt[(int64_t)t * nsum + c] * v : v;
+    }
+    row[i] = s;
+    ss += s * s;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float r = x[(int64_t)t * W + i] + row[i] * inv * (offset + w[i]);
+    x[(int64_t)t * W + i] = r;
+    if (out_cast) stf(out_cast, (int64_t)t * W + i, r);
+  }
+}
+
+// out[t][0..n) = v / sqrt(mean(v^2) + eps) * (offset + w), v = columns [col0, col0 + n) of the fp32 rows `in`
+template <typename OT>
+__global__ void rmsnorm_cols_kernel(const float* __restrict__ in, int ld, int col0, int n, const float* __restrict__ w,
+                                    float offset, float eps, OT* __restrict__ out, int ldo) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* r = in + (int64_t)t * ld + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += r[i] * r[i];
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) stf(out, (int64_t)t * ldo + i, r[i] * inv * (offset + w[i]));
+}
+
+// One warp per (token, head): out = o / sqrt(mean_P(o^2) + eps) * w[0..P) * silu(gate), gate = columns of the fp32 rows gate_src
+template <typename OT>
+__global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ldg, int gcol0,
+                                         const float* __restrict__ w, float eps, OT* __restrict__ out, int T, int H, int P) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (int64_t)T * H) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = wid / H;
+  const int h = (int)(wid - t * H);
+  const float* r = o + wid * P;
+  float ss = 0.f;
+  for (int i = lane; i < P; i += 32) ss += r[i] * r[i];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)P + eps);
+  const float* gr = gate + t * ldg + gcol0 + (int64_t)h * P;
+  for (int i = lane; i < P; i += 32) stf(out, wid * P + i, r[i] * inv * w[i] * silu_f(gr[i]));
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// gu [T, 2 ff] (gate columns first): out = act(g) * u
+template <typename OT>
+__global__ void glu_kernel(const float* __restrict__ gu, OT* __restrict__ out, int ff, int act, int64_t total) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / ff;
+    const int c = (int)(i - t * ff);
+    const float g = gu[t * 2 * ff + c], u = gu[t * 2 * ff + ff + c];
+    stf(out, i, (act == B200_ACT_GELU_TANH ? gelu_tanh_f(g) : silu_f(g)) * u);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_embed_bigram(const int32_t* tokens, const void* table, const void* bigram, int table_dtype, int buckets, int mul_prev,
+                      int mul_cur, int32_t* prev_state, const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot,
+                      const int32_t* seq_pos0, float* out, void* out_cast, int T, int W, int V, float scale, void* stream) {
+  B200_REQUIRE(tokens && table && out, "embed_bigram: null pointer");
+  B200_REQUIRE(!bigram || (buckets > 0 && prev_state && tok_seq && seq_start && seq_slot && seq_pos0),
+               "embed_bigram: the bigram table needs its bucket count, the previous-token state and the step's index tensors");
+  if (T <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(table_dtype, WT,
+                     B200_CUDA_OK(launch_kernel(embed_bigram_kernel<WT, WT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, tokens,
+                                                (const WT*)table, (const WT*)bigram, buckets, mul_prev, mul_cur, prev_state, tok_seq,
+                                                seq_start, seq_slot, seq_pos0, out, (WT*)out_cast, W, V, scale)));
+  return B200_OK;
+}
+
+int b200_rms_residual(float* x, const float* y, int nsum, const float* y_weight, const float* w, float offset, float eps,
+                      void* out_cast, int out_dtype, int T, int W, void* stream) {
+  B200_REQUIRE(x && y && w && nsum >= 1, "rms_residual: null pointer");
+  B200_REQUIRE((size_t)W * 4 <= 200 * 1024, "rms_residual: rows of %d do not fit shared memory", W);
+  if (T <= 0) return B200_OK;
+  const size_t smem = (size_t)W * 4;
+  B200_DISPATCH_ELEM(out_dtype, OT, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(rms_residual_kernel<OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_OK(launch_kernel(rms_residual_kernel<OT>, dim3(T), dim3(256), smem, (cudaStream_t)stream, x, y, nsum, y_weight, w,
+                               offset, eps, (OT*)out_cast, W));
+  });
+  return B200_OK;
+}
+
+int b200_rmsnorm_cols(const float* in, int ld, int col0, int n, const float* w, float offset, float eps, void* out, int out_dtype,
+                      int ldo, int T, void* stream) {
+  B200_REQUIRE(in && w && out && n >= 1 && ldo >= n, "rmsnorm_cols: null pointer or bad shape");
+  if (T <= 0) return B200_OK;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(rmsnorm_cols_kernel<OT>, dim3(T), dim3(n >= 1024 ? 256 : 128), 0,
+                                                (cudaStream_t)stream, in, ld, col0, n, w, offset, eps, (OT*)out, ldo)));
+  return B200_OK;
+}
+
+int b200_head_rmsnorm_gate(const float* o, const float* gate, int ldg, int gate_col0, const float* w, float eps, void* out,
+                           int out_dtype, int T, int H, int P, void* stream) {
+  B200_REQUIRE(o && gate && w && out && H >= 1 && P >= 1, "head_rmsnorm_gate: null pointer or bad shape");
+  if (T <= 0) return B200_OK;
+  const int64_t warps = (int64_t)T * H;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(head_rmsnorm_gate_kernel<OT>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0,
+                                                (cudaStream_t)stream, o, gate, ldg, gate_col0, w, eps, (OT*)out, T, H, P)));
+  return B200_OK;
+}
+
+int b200_glu(const float* gate_up, void* out, int out_dtype, int T, int ff, int act, void* stream) {
+  B200_REQUIRE(gate_up && out, "glu: null pointer");
+  B200_REQUIRE(act == B200_ACT_SILU || act == B200_ACT_GELU_TANH, "glu: activation %d", act);
+  if (T <= 0) return B200_OK;
+  const int64_t total = (int64_t)T * ff;
+  int64_t blocks = (total + 255) / 256;
+  blocks = blocks > 148 * 16 ? 148 * 16 : blocks;
+  B200_DISPATCH_ELEM(out_dtype, OT,
+                     B200_CUDA_OK(launch_kernel(glu_kernel<OT>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, gate_up,
+                                                (OT*)out, ff, act, total)));
+  return B200_OK;
+}
+
+}  // extern "C"

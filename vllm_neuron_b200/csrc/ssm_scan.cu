@@ -24,7 +24,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ in, int ld, in
   griddep_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const float bias = cb[c];
+  const float bias = cb ? cb[c] : 0.f;
   const float* wc = cw + (int64_t)c * taps;
   const int t_end = min(T, (int)(blockIdx.y + 1) * run);
   for (int t = blockIdx.y * run; t < t_end; ++t) {
@@ -350,7 +350,7 @@ extern "C" {
 int b200_causal_conv_silu(const float* in, int ld, int col0, const float* conv_w, const float* conv_b, float* state,
                           const int32_t* tok_seq, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                           void* out, int out_dtype, int T, int B, int C, int taps, void* stream) {
-  B200_REQUIRE(in && conv_w && conv_b && state && tok_seq && seq_start && seq_slot && seq_pos0 && out, "causal_conv_silu: null pointer");
+  B200_REQUIRE(in && conv_w && state && tok_seq && seq_start && seq_slot && seq_pos0 && out, "causal_conv_silu: null pointer");
   B200_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv_silu: %d taps (1..%d supported)", taps, CONV_MAX_TAPS);
   if (T <= 0 || B <= 0) return B200_OK;
   const int th = 128;

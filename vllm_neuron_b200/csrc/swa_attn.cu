@@ -7,7 +7,10 @@
 //     read through the sequence's block table.  Online softmax in fp32 that STARTS from the sink: running maximum =
 //     sink logit, running denominator = 1, accumulator = 0 -- the sink adds exp(sink) to the denominator once, has no key,
 //     no value, and is not multiplied by the score scale.
-// Pools: K [num_blocks][G][block_size][D], V [num_blocks][G][block_size][Dv] (one (block, kv head) tile is contiguous).
+//     Without a sink (sink == NULL) the softmax is the ordinary one over the visible keys.
+// Pools: K [num_blocks][G][block_size][D], V [num_blocks][G][block_size][v_pitch] with values in the first Dv columns of a
+// row (v_pitch = Dv for a pool of its own; a value pool may alias the key pool, values = the leading columns of the key
+// rows, v_pitch = D: attention over cached latents).
 #include <math.h>
 
 #include "hybrid_common.cuh"
@@ -122,7 +125,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     swa_sink_attn_kernel(const float* __restrict__ q, int ldq, const KT* __restrict__ k_pool, const KT* __restrict__ v_pool,
                          const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
                          const int32_t* __restrict__ tok_pos, const float* __restrict__ sink, float scale, int window,
-                         KT* __restrict__ out, int T, int H, int G, int D, int Dv, int bs) {
+                         KT* __restrict__ out, int T, int H, int G, int D, int Dv, int bs, int v_pitch) {
   griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) float sm_att[];
@@ -142,13 +145,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int pos = tok_pos[t];
   const int32_t* bt = block_table + (int64_t)tok_row[t] * bt_stride;
   const int lo = pos - window + 1 > 0 ? pos - window + 1 : 0;
-  const bool vvec = (Dv & 1) == 0;
+  const bool vvec = (Dv & 1) == 0 && (v_pitch & 1) == 0;
   float m[QH], l[QH];  // the sink: exp(sink - m) = 1 in the denominator, nothing in the numerator
   float2 acc[QH][MAXC];
 #pragma unroll
   for (int qh = 0; qh < QH; ++qh) {
-    m[qh] = sink[h0 + qh];
-    l[qh] = warp == 0 ? 1.0f : 0.f;
+    m[qh] = sink ? sink[h0 + qh] : -INFINITY;
+    l[qh] = sink && warp == 0 ? 1.0f : 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) acc[qh][c] = make_float2(0.f, 0.f);
   }
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       float pj[QH];
 #pragma unroll
       for (int qh = 0; qh < QH; ++qh) pj[qh] = __shfl_sync(0xffffffffu, p[qh], jj);
-      const KT* vr = v_pool + tj * Dv;
+      const KT* vr = v_pool + tj * v_pitch;
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
         const int d = 2 * lane + 64 * c;
@@ -253,15 +256,17 @@ int b200_kv_write_vmix(const float* qkv, int ld, int k_col0, int v_col0, float* 
 
 int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* v_pool, int kv_dtype, const int32_t* block_table,
                        int64_t bt_stride, const int32_t* tok_row, const int32_t* tok_pos, const float* sink, float scale,
-                       int window, void* out, int T, int H, int G, int D, int Dv, int block_size, void* stream) {
-  B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && sink && out, "swa_sink_attn: null pointer");
+                       int window, void* out, int T, int H, int G, int D, int Dv, int v_pitch, int block_size, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && tok_row && tok_pos && out, "swa_sink_attn: null pointer");
+  B200_REQUIRE(v_pitch >= Dv, "swa_sink_attn: value rows of pitch %d hold %d values", v_pitch, Dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "swa_sink_attn: %d query heads over %d kv heads", H, G);
   B200_REQUIRE(window >= 1, "swa_sink_attn: window %d", window);
-  B200_REQUIRE(Dv >= 1 && Dv <= 256 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..256", D, Dv);
+  B200_REQUIRE(Dv >= 1 && Dv <= 512 && D >= 1 && D <= 1024, "swa_sink_attn: head sizes %d / %d outside 1..1024 / 1..512", D, Dv);
   if (T <= 0) return B200_OK;
   B200_REQUIRE((int64_t)T * H < (1ll << 31), "swa_sink_attn: %d tokens x %d heads exceed the grid", T, H);
   const int rep = H / G;  // query heads per kv head; the CTA serves 4, 2 or 1 of them with one pass over the keys
   int QHr = rep % 4 == 0 ? 4 : rep % 2 == 0 ? 2 : 1;
+  if (Dv > 256 && QHr > 2) QHr = 2;  // accumulator registers: 2 heads x 512 values per lane
   while (QHr > 1 && (int64_t)T * (H / QHr) < 148) QHr /= 2;  // small steps: keep a CTA per SM before sharing key rows
   dim3 grid((unsigned)(T * (H / QHr)));
   cudaStream_t st = (cudaStream_t)stream;
@@ -274,7 +279,7 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
                                         (int)smem));                                                                         \
     B200_CUDA_OK(launch_kernel(swa_sink_attn_kernel<KT, MC, QH>, grid, dim3(ATT_WARPS * 32), smem, st, q, ldq,               \
                                (const KT*)k_pool, (const KT*)v_pool, block_table, bt_stride, tok_row, tok_pos, sink, scale, \
-                               window, (KT*)out, T, H, G, D, Dv, block_size));                                               \
+                               window, (KT*)out, T, H, G, D, Dv, block_size, v_pitch));                                               \
   } while (0)
 #define ATT_LAUNCH(MC)                \
   do {                                \
@@ -285,7 +290,8 @@ int b200_swa_sink_attn(const float* q, int ldq, const void* k_pool, const void* 
   B200_DISPATCH_ELEM(kv_dtype, KT, {
     if (Dv <= 64) ATT_LAUNCH(1);
     else if (Dv <= 128) ATT_LAUNCH(2);
-    else ATT_LAUNCH(4);
+    else if (Dv <= 256) ATT_LAUNCH(4);
+    else ATT_LAUNCH(8);
   });
 #undef ATT_LAUNCH_Q
 #undef ATT_LAUNCH

@@ -1,6 +1,7 @@
 // Tensor-core prompt-portion kernel of the sliding-window sink attention (bf16 pools): same contract as swa_sink_attn in
 // swa_attn.cu -- a query at position i attends keys i - window < j <= i through its block table, the softmax starts
-// from the per-head sink (running maximum = sink, denominator = 1, no value) -- computed FlashAttention-style.
+// from the per-head sink (running maximum = sink, denominator = 1, no value; none when sink == NULL) -- computed
+// FlashAttention-style.  Value rows have pitch v_pitch (the value pool may alias the leading columns of the key pool).
 //   CTA = 64 consecutive new tokens of one sequence x one query head, 4 warps x 16 rows.  Keys are walked in tiles of 32
 //   from the first key the tile's first row may see to the last key its last row may see; each tile's K and V rows are
 //   gathered page by page into shared memory with cp.async, one tile ahead of the MMAs (rows padded by 16 bytes:
@@ -24,7 +25,7 @@ __global__ void __launch_bounds__(128)
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ block_table, int64_t bt_stride,
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                             const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
-                            __nv_bfloat16* __restrict__ out, int H, int G, int D, int Dv, int bs) {
+                            __nv_bfloat16* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch) {
   griddep_launch();
   griddep_wait();
   const int sq = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PF_ROWS;
@@ -50,8 +51,8 @@ __global__ void __launch_bounds__(128)
   const int r_lo = 16 * warp + (lane >> 2);
   const int p_lo = pos0 + i0 + r_lo, p_hi = p_lo + 8;
   const bool ok_lo = i0 + r_lo < n, ok_hi = i0 + r_lo + 8 < n;
-  float m_lo = sink[h], m_hi = m_lo;
-  float l_lo = (lane & 3) == 0 ? 1.0f : 0.f, l_hi = l_lo;  // the sink's share of the denominator, counted once per row
+  float m_lo = sink ? sink[h] : -INFINITY, m_hi = m_lo;
+  float l_lo = sink && (lane & 3) == 0 ? 1.0f : 0.f, l_hi = l_lo;  // the sink's share of the denominator, counted once per row
   float o[2 * DV16M][4];
 #pragma unroll
   for (int j = 0; j < 2 * DV16M; ++j)
@@ -72,7 +73,7 @@ __global__ void __launch_bounds__(128)
       const bool ok = j <= j_hi;
       const int64_t row = ok ? ((int64_t)bt[j / bs] * G + g) * bs + (j % bs) : 0;
       if (c < kch) cp_async16(smem_u32(Kd + r * ldk + c * 8), k_pool + row * D + c * 8, ok);
-      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + row * Dv + (c - kch) * 8, ok);
+      else cp_async16(smem_u32(Vd + r * ldv + (c - kch) * 8), v_pool + row * v_pitch + (c - kch) * 8, ok);
     }
     cp_async_commit();  // an empty group past the last tile keeps the wait counts uniform
   };
@@ -124,7 +125,8 @@ __global__ void __launch_bounds__(128)
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
     const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-    const float c_lo = __expf(m_lo - mn_lo), c_hi = __expf(m_hi - mn_hi);
+    // a row that has seen no key yet (no sink, every key of the tile masked) keeps m = -inf: nothing to rescale
+    const float c_lo = mn_lo == -INFINITY ? 1.0f : __expf(m_lo - mn_lo), c_hi = mn_hi == -INFINITY ? 1.0f : __expf(m_hi - mn_hi);
     m_lo = mn_lo;
     m_hi = mn_hi;
     l_lo *= c_lo;
@@ -132,8 +134,8 @@ __global__ void __launch_bounds__(128)
     uint32_t pf[4][2];  // P as bf16 pairs: [n8 tile][row half]
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float p0 = __expf(s[j][0] - mn_lo), p1 = __expf(s[j][1] - mn_lo);
-      const float p2 = __expf(s[j][2] - mn_hi), p3 = __expf(s[j][3] - mn_hi);
+      const float p0 = mn_lo == -INFINITY ? 0.f : __expf(s[j][0] - mn_lo), p1 = mn_lo == -INFINITY ? 0.f : __expf(s[j][1] - mn_lo);
+      const float p2 = mn_hi == -INFINITY ? 0.f : __expf(s[j][2] - mn_hi), p3 = mn_hi == -INFINITY ? 0.f : __expf(s[j][3] - mn_hi);
       l_lo += p0 + p1;
       l_hi += p2 + p3;
       pf[j][0] = pack_bf16(p0, p1);
@@ -191,11 +193,11 @@ extern "C" {
 int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                int64_t bt_stride, const int32_t* seq_start, const int32_t* seq_slot, const int32_t* seq_pos0,
                                int B, int max_new, const float* sink, float scale, int window, void* out, int H, int G, int D,
-                               int Dv, int block_size, void* stream) {
-  B200_REQUIRE(q && k_pool && v_pool && block_table && seq_start && seq_slot && seq_pos0 && sink && out,
+                               int Dv, int v_pitch, int block_size, void* stream) {
+  B200_REQUIRE(q && k_pool && v_pool && block_table && seq_start && seq_slot && seq_pos0 && out,
                "swa_sink_attn_prefill: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && window >= 1, "swa_sink_attn_prefill: %d query heads over %d kv heads", H, G);
-  if (D % 16 || Dv % 16 || Dv > 256 || D > 512 || (ldq & 1) || ((uintptr_t)q & 7)) {
+  if (D % 16 || Dv % 16 || Dv > 256 || D > 512 || v_pitch % 8 || v_pitch < Dv || (ldq & 1) || ((uintptr_t)q & 7)) {
     set_last_error("swa_sink_attn_prefill: head sizes %d / %d need multiples of 16 (<= 512 / 256)", D, Dv);
     return B200_ERR_UNSUPPORTED;
   }
@@ -210,7 +212,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
       B200_CUDA_OK(cudaFuncSetAttribute(swa_sink_prefill_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     B200_CUDA_OK(launch_kernel(swa_sink_prefill_kernel<M>, grid, dim3(128), smem, st, q, ldq, (const BT*)k_pool,              \
                                (const BT*)v_pool, block_table, bt_stride, seq_start, seq_slot, seq_pos0, sink, scale, window, \
-                               (BT*)out, H, G, D, Dv, block_size));                                                           \
+                               (BT*)out, H, G, D, Dv, block_size, v_pitch));                                                           \
   } while (0)
   if (Dv <= 64) PF_LAUNCH(4);
   else if (Dv <= 128) PF_LAUNCH(8);

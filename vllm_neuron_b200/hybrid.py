@@ -14,6 +14,23 @@ Feed-forward: sigmoid router, `top` experts by score, weights = scores (not reno
 experts down((b + 1) a / (1 + exp(-1.702 a))) with a = min(gate(h), L), b = clip(up(h), -L, L), plus an always-on shared
 expert.  Every size and constant above is read from the configuration.
 
+A second block style, post-norm RMS (the "Kenetar" design), shares the step, the pools and the state slots:
+  x += R1(mixer(x));  x += R2(ff(x))   with R(y) = y / sqrt(mean(y^2) + eps) * (1 + w); the sublayers read x itself.  The
+embedding is table[token] * scale plus a hashed bigram row (the previous token is per-sequence state); the logits are
+head . Rf(x) * logit_scale.  Mixers:
+  * 'delta'            -- q / k / v projections, each through a short causal convolution + SiLU; q and k unit vectors per key
+                          head (q also / sqrt(dim)); beta = sigmoid(b h), decay g = exp(-exp(A_log) softplus(a h + dt_bias));
+                          gated delta rule  S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q  per head; per-head RMS
+                          norm of o, times silu(g h), out-projection.  State per sequence: S (fp32) and the last taps - 1
+                          convolution inputs.
+  * 'latent_attention' -- queries through a normed latent (dq, uq), keys and values as up-projections (uk, uv) of ONE
+                          normed latent c per token plus one rotated key part shared by the heads; interleaved-pair rotary
+                          angles with YaRN frequency blending; causal softmax; a per-head sigmoid output gate.  Cached per
+                          token: [c | rotated key part]; attention runs in the latent space (uk folded into the query, uv
+                          applied to the attended latent).
+Feed-forward: dense W_down(gelu_tanh(W_gate h) * W_up h), or SiLU experts chosen by the `top` largest router logits (+ bias)
+and weighed, on their OUTPUTS, by the softmax over the chosen logits.
+
 The step is ONE ragged batch (`StepMeta`): portions of prompts and single decoded tokens run through the same kernels, each
 sequence continuing from its KV pages (block table row) and its state slot.  fp32 everywhere the design asks for it
 (residual stream, norms, softmax, router, recurrence); GEMM operands, weights and KV pools are bf16, or fp32 when the model is
@@ -27,9 +44,13 @@ from dataclasses import dataclass, field
 
 import torch
 
+import math
+
 from . import ops
 
 ARCHITECTURE = "Pumopel"
+# block style per architecture: how the norms sit around the sublayers (and which norm it is)
+BLOCK_STYLES = {"Pumopel": "dyt_sandwich", "Kenetar": "rms_post"}
 _NO_WINDOW = 1 << 30
 
 
@@ -68,13 +89,76 @@ class AttnSpec:
 
 
 @dataclass
+class DeltaSpec:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+    @property
+    def channels(self) -> int:  # what the convolution sees: [q | k | v]
+        return 2 * self.kv_heads * self.dim + self.heads * self.vdim
+
+    @property
+    def proj(self) -> int:  # rows of the in-projection: [q | k | v | b | a | g]
+        return self.channels + 2 * self.heads + self.heads * self.vdim
+
+
+@dataclass
+class RotSpec:
+    """Rotary angles of interleaved pairs over the first `dims` columns; `scaling` (YaRN): factor, original, fast, slow."""
+    dims: int
+    base: float
+    scaling: dict | None = None
+
+    def tables(self, positions: int):
+        """(cos, sin) fp32 [positions, dims / 2], computed in float64.  Pair i turns by p * f_i, f_i = base^(-2i/dims); with
+        scaling, f_i is blended with f_i / factor by a linear ramp between the pair indices where `fast` and `slow` full turns
+        fit into `original` positions, and cos / sin carry the factor 0.1 ln(factor) + 1."""
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = self.base ** (-2.0 * i / self.dims)
+        mscale = 1.0
+        sc = self.scaling
+        if sc:
+            turns_at = lambda turns: self.dims * math.log(sc["original"] / (2 * math.pi * turns)) / (2 * math.log(self.base))
+            lo = max(math.floor(turns_at(sc["fast"])), 0)
+            hi = min(math.ceil(turns_at(sc["slow"])), self.dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0, 1)
+            f = f / sc["factor"] * ramp + f * (1 - ramp)
+            mscale = 0.1 * math.log(sc["factor"]) + 1.0
+        a = torch.arange(positions, dtype=torch.float64)[:, None] * f
+        return (torch.cos(a) * mscale).float().contiguous(), (torch.sin(a) * mscale).float().contiguous()
+
+
+@dataclass
+class LatentAttnSpec:
+    heads: int
+    dim: int       # unrotated query / key columns per head
+    rot_dim: int   # rotated columns per head (the key's are shared by the heads)
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot: RotSpec = None
+
+
+@dataclass
 class MoeSpec:
     experts: int
     top: int
     ff: int
-    limit: float
+    limit: float = 0.0
     shared_ff: int = 0
     shared_limit: float = 0.0
+    # 'sigmoid_in': weights = sigmoid scores applied to the expert's input, clamped-swish experts;
+    # 'softmax_out': weights = softmax over the chosen logits (+ router bias) applied to the experts' outputs, SiLU experts
+    route: str = "sigmoid_in"
+
+
+@dataclass
+class DenseSpec:
+    ff: int
 
 
 @dataclass
@@ -92,10 +176,20 @@ class HybridConfig:
     embed_scale: float
     layers: list = field(default_factory=list)
     name: str = ARCHITECTURE
+    bigram: dict | None = None   # buckets, mul_prev, mul_cur
+    logit_scale: float = 1.0
+
+    @property
+    def style(self) -> str:
+        return BLOCK_STYLES[self.name]
 
     @staticmethod
     def from_dict(d: dict) -> "HybridConfig":
         layers = []
+        name = d.get("architecture", ARCHITECTURE)
+        if name not in BLOCK_STYLES:
+            raise ValueError(f"unknown hybrid architecture {name!r}")
+        post = BLOCK_STYLES[name] == "rms_post"
         for L in d["layers"]:
             m = L["mixer"]
             if L["type"] == "mamba2":
@@ -109,19 +203,41 @@ class HybridConfig:
                                  int(mask.get("size", _NO_WINDOW)), bool(m.get("v_mix", False)))
                 if mixer.heads % mixer.kv_heads:
                     raise ValueError(f"attention layer: {mixer.heads} query heads over {mixer.kv_heads} kv heads")
+            elif L["type"] == "delta":
+                mixer = DeltaSpec(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m["conv"]))
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f"delta layer: {mixer.heads} heads over {mixer.kv_heads} key heads")
+            elif L["type"] == "latent_attention":
+                r = m["rot"]
+                mixer = LatentAttnSpec(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]),
+                                       int(m["q_rank"]), float(m["scale"]),
+                                       RotSpec(int(r["dims"]), float(r["base"]), dict(r["scaling"]) if r.get("scaling") else None))
+                if mixer.rot.dims > mixer.rot_dim or mixer.rot.dims % 2:
+                    raise ValueError(f"latent attention: {mixer.rot.dims} rotating columns in a rotated part of {mixer.rot_dim}")
             else:
                 raise ValueError(f"unknown layer type {L['type']!r}")
+            if post != (L["type"] in ("delta", "latent_attention")):
+                raise ValueError(f"layer type {L['type']!r} is not part of the {name} design")
             f = L.get("mlp")
             mlp = None
             if f:
-                if f.get("kind", "moe") != "moe":
-                    raise ValueError(f"unknown feed-forward kind {f.get('kind')!r}")
-                sh = f.get("shared") or {}
-                mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
-                              float(f["expert"]["limit"]), int(sh.get("ff", 0)), float(sh.get("limit", 0.0)))
+                kind = f.get("kind", "moe")
+                if kind == "dense" and post:
+                    mlp = DenseSpec(int(f["ff"]))
+                elif kind == "moe" and post:
+                    mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]), route="softmax_out")
+                elif kind == "moe":
+                    sh = f.get("shared") or {}
+                    mlp = MoeSpec(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
+                                  float(f["expert"]["limit"]), int(sh.get("ff", 0)), float(sh.get("limit", 0.0)))
+                else:
+                    raise ValueError(f"unknown feed-forward kind {kind!r}")
             layers.append(LayerSpec(L["type"], mixer, mlp))
-        return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(d["embedding"]["scale"]), layers,
-                            d.get("architecture", ARCHITECTURE))
+        emb = d["embedding"]
+        big = emb.get("bigram")
+        return HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(emb["scale"]), layers, name,
+                            {k: int(big[k]) for k in ("buckets", "mul_prev", "mul_cur")} if big else None,
+                            float(d.get("logit_scale", 1.0)))
 
     @staticmethod
     def from_pretrained(path: str) -> "HybridConfig":
@@ -132,9 +248,19 @@ class HybridConfig:
         """The configuration in its file form (what from_dict reads)."""
         out = {"architecture": self.name, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.eps},
                "embedding": {"scale": self.embed_scale}, "layers": []}
+        if self.bigram:
+            out["embedding"]["bigram"] = dict(self.bigram)
+        if self.style == "rms_post":
+            out["logit_scale"] = self.logit_scale
         for L in self.layers:
             m = L.mixer
-            if L.kind == "mamba2":
+            if L.kind == "delta":
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "conv": m.conv}
+            elif L.kind == "latent_attention":
+                mixer = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank,
+                         "q_rank": m.q_rank, "scale": m.scale,
+                         "rot": {"dims": m.rot.dims, "base": m.rot.base, "scaling": dict(m.rot.scaling) if m.rot.scaling else None}}
+            elif L.kind == "mamba2":
                 mixer = {"heads": m.heads, "vdim": m.vdim, "state": m.state, "groups": m.groups, "conv": m.conv,
                          "norm_groups": m.norm_groups}
             else:
@@ -143,7 +269,11 @@ class HybridConfig:
                 if m.window != _NO_WINDOW:
                     mixer["mask"] = {"size": m.window}
             f = None
-            if L.mlp:
+            if isinstance(L.mlp, DenseSpec):
+                f = {"kind": "dense", "ff": L.mlp.ff}
+            elif L.mlp and L.mlp.route == "softmax_out":
+                f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top}, "expert": {"ff": L.mlp.ff}}
+            elif L.mlp:
                 f = {"kind": "moe", "router": {"experts": L.mlp.experts, "top": L.mlp.top},
                      "expert": {"ff": L.mlp.ff, "limit": L.mlp.limit},
                      "shared": {"ff": L.mlp.shared_ff, "limit": L.mlp.shared_limit} if L.mlp.shared_ff else None}
@@ -155,17 +285,34 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
     """Checkpoint tensor name -> shape (a linear layer's matrix has one row per output)."""
     W = cfg.width
     s: dict[str, tuple] = {"embed": (cfg.vocab, W), "head": (cfg.vocab, W)}
+    post = cfg.style == "rms_post"
+    if cfg.bigram:
+        s["bigram"] = (cfg.bigram["buckets"] + 1, W)
 
     def norm(n):
-        s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
+        if post:
+            s[n] = (W,)
+        else:
+            s[n], s[n + ".b"], s[n + ".alpha"] = (W,), (W,), ()
 
     norm("final.norm")
     for i, L in enumerate(cfg.layers):
         p = f"l{i}."
-        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ()):
+        for n in (("norm1",) + (("norm2",) if L.mlp else ())) if post else (("norm1", "norm1b") + (("norm2", "norm2b") if L.mlp else ())):
             norm(p + n)
         m = L.mixer
-        if L.kind == "mamba2":
+        if L.kind == "delta":
+            gd, hp = m.kv_heads * m.dim, m.heads * m.vdim
+            s.update({p + "mix.q": (gd, W), p + "mix.q.conv": (gd, m.conv), p + "mix.k": (gd, W), p + "mix.k.conv": (gd, m.conv),
+                      p + "mix.v": (hp, W), p + "mix.v.conv": (hp, m.conv), p + "mix.b": (m.heads, W), p + "mix.a": (m.heads, W),
+                      p + "mix.A_log": (m.heads,), p + "mix.dt_bias": (m.heads,), p + "mix.norm": (m.vdim,),
+                      p + "mix.g": (hp, W), p + "mix.o": (W, hp)})
+        elif L.kind == "latent_attention":
+            s.update({p + "mix.dq": (m.q_rank, W), p + "mix.dq.norm": (m.q_rank,),
+                      p + "mix.uq": (m.heads * (m.dim + m.rot_dim), m.q_rank), p + "mix.dkv": (m.kv_rank + m.rot_dim, W),
+                      p + "mix.dkv.norm": (m.kv_rank,), p + "mix.uk": (m.heads * m.dim, m.kv_rank),
+                      p + "mix.uv": (m.heads * m.vdim, m.kv_rank), p + "mix.g": (m.heads, W), p + "mix.o": (W, m.heads * m.vdim)})
+        elif L.kind == "mamba2":
             s.update({p + "mix.in": (m.proj, W), p + "mix.conv": (m.channels, m.conv), p + "mix.conv.b": (m.channels,),
                       p + "mix.dt_bias": (m.heads,), p + "mix.A_log": (m.heads,), p + "mix.D": (m.heads,),
                       p + "mix.norm": (m.inner,), p + "mix.o": (W, m.inner)})
@@ -175,8 +322,12 @@ def tensor_shapes(cfg: HybridConfig) -> dict[str, tuple]:
             if m.v_mix:
                 s[p + "mix.vmix"] = ()
         f = L.mlp
-        if f:
+        if isinstance(f, DenseSpec):
+            s.update({p + "mlp.gate": (f.ff, W), p + "mlp.up": (f.ff, W), p + "mlp.down": (W, f.ff)})
+        elif f:
             s[p + "mlp.router"] = (f.experts, W)
+            if f.route == "softmax_out":
+                s[p + "mlp.router.b"] = (f.experts,)
             for e in range(f.experts):
                 s.update({f"{p}mlp.e{e}.gate": (f.ff, W), f"{p}mlp.e{e}.up": (f.ff, W), f"{p}mlp.e{e}.down": (W, f.ff)})
             if f.shared_ff:
@@ -189,9 +340,12 @@ def random_weights(cfg: HybridConfig, seed: int = 0, std: float | None = None) -
     """Seeded random weights under the checkpoint names (bf16), scaled so that activations stay O(1) through the layers."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     out = {}
+    post = cfg.style == "rms_post"
     for name, shape in tensor_shapes(cfg).items():
         leaf = name.rsplit(".", 1)[-1]
-        if leaf == "alpha":
+        if post and leaf in ("norm1", "norm2") or (post and name == "final.norm"):
+            t = 0.1 * torch.randn(shape, generator=g)  # stored around zero: the norm multiplies by 1 + w
+        elif leaf == "alpha":
             t = 0.5 + 0.5 * torch.rand((), generator=g)
         elif leaf == "vmix":
             t = 0.2 + 0.5 * torch.rand((), generator=g)
@@ -323,18 +477,49 @@ class HybridCausalLM:
         def vec(name):
             return get(name).to(dev, torch.float32).contiguous()
 
+        post = cfg.style == "rms_post"
+
         def norm(name):
+            if post:  # RMS norm, weight stored around zero
+                return vec(name)
             return (vec(name), vec(name + ".b"), float(get(name + ".alpha").float()))
 
         self.embed, self.head = lin("embed"), lin("head")
         self.final_norm = norm("final.norm")
         self.layers = []
         slots = max_num_seqs + 1
+        self.bigram = self.prev_token = None
+        if cfg.bigram:
+            self.bigram = lin("bigram")
+            self.prev_token = torch.zeros((slots,), dtype=torch.int32, device=dev)  # each sequence's last token
+        if post:  # the logit scale rides on the final norm's factor: (1 + w) * logit_scale
+            self.final_norm_scaled = (self.final_norm * cfg.logit_scale).contiguous()
+        rot_tables: dict = {}
         first_vmix = True
         for i, L in enumerate(cfg.layers):
             p, m = f"l{i}.", L.mixer
-            lw = {"spec": L, "norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b")}
-            if L.kind == "mamba2":
+            lw = {"spec": L, "norm1": norm(p + "norm1")}
+            if not post:
+                lw["norm1b"] = norm(p + "norm1b")
+            if L.kind == "delta":
+                lw.update(w_in=lin(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.b", p + "mix.a", p + "mix.g"),
+                          conv_w=torch.cat([get(p + "mix.q.conv"), get(p + "mix.k.conv"), get(p + "mix.v.conv")]
+                                           ).to(dev, torch.float32).contiguous(),
+                          a_log=vec(p + "mix.A_log"), dt_bias=vec(p + "mix.dt_bias"), onorm=vec(p + "mix.norm"),
+                          w_o=lin(p + "mix.o"),
+                          conv_state=torch.zeros((slots, max(m.conv - 1, 1), m.channels), dtype=torch.float32, device=dev),
+                          delta_state=torch.zeros((slots, m.heads, m.vdim, m.dim), dtype=torch.float32, device=dev))
+            elif L.kind == "latent_attention":
+                key = (m.rot.dims, m.rot.base, json.dumps(m.rot.scaling, sort_keys=True))
+                if key not in rot_tables:
+                    rot_tables[key] = tuple(t.to(dev) for t in m.rot.tables(self.max_blocks * block_size))
+                lw.update(w_in=lin(p + "mix.dq", p + "mix.dkv", p + "mix.g"), dq_norm=vec(p + "mix.dq.norm"),
+                          dkv_norm=vec(p + "mix.dkv.norm"), w_uq=lin(p + "mix.uq"), w_o=lin(p + "mix.o"), rot=rot_tables[key],
+                          # per head: the key up-projection transposed (it is folded into the query), the value up-projection
+                          w_absorb=get(p + "mix.uk").view(m.heads, m.dim, m.kv_rank).transpose(1, 2).to(dev, et).contiguous(),
+                          w_uv=get(p + "mix.uv").view(m.heads, m.vdim, m.kv_rank).to(dev, et).contiguous(),
+                          k_pool=torch.zeros((num_blocks, 1, block_size, m.kv_rank + m.rot_dim), dtype=et, device=dev))
+            elif L.kind == "mamba2":
                 lw.update(w_in=lin(p + "mix.in"), conv_w=vec(p + "mix.conv"), conv_b=vec(p + "mix.conv.b"),
                           dt_bias=vec(p + "mix.dt_bias"), a_log=vec(p + "mix.A_log"), d=vec(p + "mix.D"),
                           gnorm=vec(p + "mix.norm"), w_o=lin(p + "mix.o"),
@@ -356,7 +541,15 @@ class HybridCausalLM:
                     first_vmix = False
             f = L.mlp
             if f:
-                lw.update(norm2=norm(p + "norm2"), norm2b=norm(p + "norm2b"), w_router=lin(p + "mlp.router"))
+                lw["norm2"] = norm(p + "norm2")
+                if not post:
+                    lw["norm2b"] = norm(p + "norm2b")
+            if isinstance(f, DenseSpec):
+                lw.update(w_gu=lin(p + "mlp.gate", p + "mlp.up"), w_down=lin(p + "mlp.down"))
+            elif f:
+                lw["w_router"] = lin(p + "mlp.router")
+                if f.route == "softmax_out":
+                    lw["router_b"] = vec(p + "mlp.router.b")
                 lw["w_gu"] = torch.stack([torch.cat([get(f"{p}mlp.e{e}.gate"), get(f"{p}mlp.e{e}.up")]) for e in range(f.experts)]
                                          ).to(dev, et).contiguous()
                 lw["w_down"] = torch.stack([get(f"{p}mlp.e{e}.down") for e in range(f.experts)]).to(dev, et).contiguous()
@@ -374,11 +567,14 @@ class HybridCausalLM:
     def kv_bytes_per_block(self) -> int:
         es = 2 if self.et == torch.bfloat16 else 4
         return sum(L.mixer.kv_heads * self.block_size * (L.mixer.dim + L.mixer.vdim) * es
-                   for L in self.cfg.layers if L.kind == "attention")
+                   for L in self.cfg.layers if L.kind == "attention") + \
+            sum(self.block_size * (L.mixer.kv_rank + L.mixer.rot_dim) * es for L in self.cfg.layers if L.kind == "latent_attention")
 
     def state_bytes_per_slot(self) -> int:
         return sum(4 * (L.mixer.heads * L.mixer.state * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
-                   for L in self.cfg.layers if L.kind == "mamba2")
+                   for L in self.cfg.layers if L.kind == "mamba2") + \
+            sum(4 * (L.mixer.heads * L.mixer.dim * L.mixer.vdim + (L.mixer.conv - 1) * L.mixer.channels)
+                for L in self.cfg.layers if L.kind == "delta") + (4 if self.cfg.bigram else 0)
 
     # ------------------------------------------------------------------ building blocks
     def _linear(self, a, w):
@@ -416,6 +612,65 @@ class HybridCausalLM:
                               min(m.window, _NO_WINDOW))
         return self._linear(a, lw["w_o"])
 
+    def _delta(self, lw, h, meta):
+        m = lw["spec"].mixer
+        c = m.channels
+        proj = self._linear(h, lw["w_in"])  # fp32 [T, q | k | v | b | a | g]
+        qkv = ops.causal_conv_silu(proj, 0, c, lw["conv_w"], None, lw["conv_state"], meta, torch.float32)
+        o = ops.delta_rule(qkv, proj, c, c + m.heads, lw["a_log"], lw["dt_bias"], lw["delta_state"], meta, m.heads, m.kv_heads,
+                           m.dim, m.vdim, m.dim ** -0.5)
+        return self._linear(ops.head_rmsnorm_gate(o, proj, c + 2 * m.heads, lw["onorm"], self.cfg.eps, m.heads, self.et), lw["w_o"])
+
+    def _latent_attention(self, lw, h, meta):
+        m = lw["spec"].mixer
+        cos, sin = lw["rot"]
+        kr = m.kv_rank + m.rot_dim
+        proj = self._linear(h, lw["w_in"])  # fp32 [T, query latent | kv latent | shared rotated key part | head gates]
+        ops.latent_kv_write(proj, m.q_rank, m.kv_rank, m.rot_dim, m.rot.dims, lw["dkv_norm"], self.cfg.eps, cos, sin, meta,
+                            lw["k_pool"])
+        cq = ops.rmsnorm_cols(proj, 0, m.q_rank, lw["dq_norm"], self.cfg.eps, self.et)
+        q = self._linear(cq, lw["w_uq"])  # fp32 [T, H * (dim + rot_dim)]
+        nope, q_att = ops.latent_q_prep(q, m.heads, m.dim, m.rot_dim, m.rot.dims, m.kv_rank, cos, sin, meta, self.et)
+        ops.batched_linear(nope, lw["w_absorb"], q_att, a_batch_stride=m.dim, out_batch_stride=kr)
+        lat = ops.swa_sink_attn(q_att, m.heads, lw["k_pool"], None, self.block_table, meta, None, m.scale, _NO_WINDOW,
+                                latent_values=m.kv_rank)  # [T, H * kv_rank]
+        vals = torch.empty((h.shape[0], m.heads * m.vdim), dtype=self.et, device=self.device)
+        ops.batched_linear(lat, lw["w_uv"], vals, a_batch_stride=m.kv_rank, out_batch_stride=m.vdim,
+                           gate=proj[:, m.q_rank + kr:])
+        return self._linear(vals, lw["w_o"])
+
+    def _post_ff(self, lw, h):
+        """Feed-forward of the post-norm style -> (fp32 branch rows, rows per token, their weights or None)."""
+        f = lw["spec"].mlp
+        if isinstance(f, DenseSpec):
+            return self._linear(ops.glu(self._linear(h, lw["w_gu"]), ops.ACT_GELU_TANH, self.et), lw["w_down"]), 1, None
+        idx, wt = ops.moe_topk(self._linear(h, lw["w_router"]), f.top, bias=lw["router_b"], mode=ops.ROUTE_SOFTMAX_TOP)
+        align = ops.moe_align(idx, f.experts, ops.moe_wide_tiles(h, lw["w_gu"], idx.numel()))
+        pairs = ops.moe_experts(h, wt, align, lw["w_gu"], lw["w_down"], f.top, act=ops.ACT_SILU, scale_input=False)
+        return pairs, f.top, wt
+
+    def _forward_post(self, tokens, meta, logit_rows, capture):
+        """x += R1(mixer(x)); x += R2(ff(x)): every sublayer reads the residual stream itself (rounded to the operand type)."""
+        et, cfg = self.et, self.cfg
+        b = cfg.bigram or {}
+        x, h = ops.embed_bigram(tokens, self.embed, cfg.embed_scale, meta, bigram=self.bigram, buckets=b.get("buckets", 0),
+                                mul_prev=b.get("mul_prev", 0), mul_cur=b.get("mul_cur", 0), prev_state=self.prev_token)
+        for lw in self.layers:
+            y = self._delta(lw, h, meta) if lw["spec"].kind == "delta" else self._latent_attention(lw, h, meta)
+            h = ops.rms_residual(x, y, lw["norm1"], cfg.eps, out_dtype=et)
+            if lw["spec"].mlp:
+                y, nsum, wt = self._post_ff(lw, h)
+                h = ops.rms_residual(x, y, lw["norm2"], cfg.eps, nsum=nsum, y_weight=wt, out_dtype=et)
+            if capture is not None:
+                capture.append(x.clone())
+        if logit_rows is None or logit_rows.numel() == 0:
+            self.last_logits = None
+            return None
+        hf = ops.rmsnorm_cols(x.index_select(0, logit_rows).contiguous(), 0, cfg.width, self.final_norm_scaled, cfg.eps, et,
+                              offset=cfg.logit_scale)
+        self.last_logits = self._linear(hf, self.head)
+        return self.last_logits
+
     def _moe(self, lw, h):
         f = lw["spec"].mlp
         idx, wt = ops.moe_topk(self._linear(h, lw["w_router"]), f.top)  # fp32 logits, sigmoid scores
@@ -431,6 +686,8 @@ class HybridCausalLM:
         """tokens int32 [T] (device) of the ragged batch `meta`; returns fp32 logits [len(logit_rows), vocab] (None when no
         row is asked for).  KV pools and recurrent state of the sequences advance by the step's tokens.
         capture: a list that is given, layer by layer, a copy of x as that layer leaves it."""
+        if self.cfg.style == "rms_post":
+            return self._forward_post(tokens, meta, logit_rows, capture)
         et, n = self.et, len(self.layers)
         x = ops.embed_scale(tokens, self.embed, self.cfg.embed_scale)
         h = ops.dyt_norm(x, *self.layers[0]["norm1"], et) if n else None

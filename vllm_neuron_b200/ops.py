@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import _cabi
-from ._cabi import BF16, F32, FP8_E4M3, INT8, check
+from ._cabi import ACT_GELU_TANH, ACT_SILU, ACT_SWISH_CLAMPED, BF16, F32, FP8_E4M3, INT8, ROUTE_SIGMOID, ROUTE_SOFTMAX_TOP, check
 
 _QDT = {None: BF16, "bf16": BF16, "fp8": FP8_E4M3, "int8": INT8}
 _TORCH_Q = {FP8_E4M3: torch.float8_e4m3fn, INT8: torch.int8}
@@ -674,7 +674,7 @@ def clamped_glu(gate_up, limit: float, out_dtype):
 def causal_conv_silu(src, col0: int, channels: int, conv_w, conv_b, state, meta, out_dtype):
     """Columns [col0, col0 + channels) of the fp32 rows `src` -> SiLU(conv) [T, channels]; `state` [slots, taps-1, channels]
     fp32 is read for continuing sequences and updated for all."""
-    _cuda(src, conv_w, conv_b, state)
+    _cuda(src, conv_w, conv_b, state)  # conv_b may be None (no bias)
     _f32(src, conv_w, conv_b, state)
     t, taps = src.shape[0], conv_w.shape[1]
     assert conv_w.shape[0] == channels and state.shape[1:] == (max(taps - 1, 1), channels)  # one unused row when taps == 1
@@ -730,13 +730,20 @@ def kv_write_vmix(qkv, k_col0: int, v_col0: int, k_pool, v_pool, slot_mapping, *
 PREFILL_ATTN_MIN_TOKENS = 16  # longest portion of a step from which the tensor-core attention kernel is used
 
 
-def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int):
-    """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type."""
+def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink, scale: float, window: int,
+                  latent_values: int = 0):
+    """q = the first num_heads * D columns of the fp32 rows q_src -> [T, num_heads * Dv] in the pools' element type.
+    sink None: ordinary softmax.  latent_values = C > 0: v_pool is ignored and the values are the first C columns of the key
+    rows (attention over cached latents: one pool holds both)."""
     _cuda(q_src, k_pool, v_pool, block_table, sink)
     _f32(q_src, sink)
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     _, g, bs, d = k_pool.shape
-    dv = v_pool.shape[3]
+    if latent_values:
+        v_pool, dv, v_pitch = k_pool, int(latent_values), d
+        assert g == 1 and dv <= d
+    else:
+        dv = v_pitch = v_pool.shape[3]
     t = q_src.shape[0]
     out = torch.empty((t, num_heads * dv), dtype=k_pool.dtype, device=q_src.device)
     # prompt portions in bf16 serving: the tensor-core kernel; decode-sized steps, fp32 pools and odd head sizes: one CTA per
@@ -747,26 +754,29 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
             check(_cabi.load().b200_swa_sink_attn_prefill(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                                           block_table.stride(0), _ptr(meta.seq_start), _ptr(meta.seq_slot),
                                                           _ptr(meta.seq_pos0), meta.num_seqs, meta.max_new, _ptr(sink), float(scale),
-                                                          int(window), _ptr(out), num_heads, g, d, dv, bs, _stream()),
+                                                          int(window), _ptr(out), num_heads, g, d, dv, v_pitch, bs, _stream()),
                   "b200_swa_sink_attn_prefill")
         return out
     with _k("swa_sink_attn"):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
-                                              _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, bs,
+                                              _ptr(sink), float(scale), int(window), _ptr(out), t, num_heads, g, d, dv, v_pitch, bs,
                                               _stream()), "b200_swa_sink_attn")
     return out
 
 
-def moe_topk(logits, top: int):
-    """fp32 router logits [T, E] -> (expert ids int32 [T, top], routing weights fp32 [T, top] = sigmoid of the chosen logits)."""
-    _cuda(logits)
+def moe_topk(logits, top: int, bias=None, mode: int = ROUTE_SIGMOID):
+    """fp32 router logits [T, E] (+ bias fp32 [E]) -> (expert ids int32 [T, top], routing weights fp32 [T, top]): the sigmoid of
+    each chosen logit (ROUTE_SIGMOID) or the softmax over the chosen logits (ROUTE_SOFTMAX_TOP)."""
+    _cuda(logits, bias)
+    _f32(bias)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     t, e = logits.shape
     idx = torch.empty((t, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((t, top), dtype=torch.float32, device=logits.device)
     with _k("moe_topk"):
-        check(_cabi.load().b200_moe_topk(_ptr(logits), logits.stride(0), _ptr(idx), _ptr(wt), t, e, top, _stream()), "b200_moe_topk")
+        check(_cabi.load().b200_moe_topk(_ptr(logits), logits.stride(0), _ptr(bias), int(mode), _ptr(idx), _ptr(wt), t, e, top,
+                                         _stream()), "b200_moe_topk")
     return idx, wt
 
 
@@ -810,35 +820,180 @@ def linear_simt(a, w):
     out = torch.empty((m, n), dtype=torch.float32, device=a.device)
     with _k(f"linear_simt[{m}x{n}x{k}]"):
         check(_cabi.load().b200_grouped_linear(_ptr(a), a.stride(0), 0, 0, 0, _ptr(w), 0, 0, 0, -(-m // moe_tile_rows()), m, n, k,
-                                               _edt(a), _ptr(out), n, 0, 0, 0.0, moe_tile_rows(), _stream()), "b200_grouped_linear")
+                                               _edt(a), _ptr(out), n, 0, 0, 0, 0.0, moe_tile_rows(), _stream()), "b200_grouped_linear")
     return out
 
 
-def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float):
-    """Routed experts: for every (token, choice) pair  W_down glu(W_gate_up (weight * h)).  h [T, W]; w_gate_up
-    [E, 2 ff, W] (gate rows first), w_down [E, W, ff]; returns fp32 [T * top, W] in pair order."""
+def batched_linear(a, w, out, *, a_batch_stride: int, out_batch_stride: int, gate=None):
+    """out_b = a_b @ w[b]^T for every b of w [batch, N, K] in one launch: a_b = rows of `a` (pitch a.stride(0)) starting at
+    column b * a_batch_stride, out_b likewise in `out` (fp32, or the operand type).  gate: fp32 view [M, >= batch] whose
+    sigmoid multiplies out_b's rows."""
+    _cuda(a, w, out, gate)
+    assert a.dtype == w.dtype and a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous() and w.dim() == 3
+    b, n, k = w.shape
+    m = a.shape[0]
+    typed = out.dtype == a.dtype and out.dtype != torch.float32
+    assert typed or out.dtype == torch.float32
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == m
+    with _k(f"batched_linear[{b}x{m}x{n}x{k}]"):
+        check(_cabi.load().b200_batched_linear(_ptr(a), a.stride(0), a_batch_stride, _ptr(w), n * k, _ptr(out), out.stride(0),
+                                               out_batch_stride, b, m, n, k, _edt(a), 1 if typed else 0, _ptr(gate),
+                                               gate.stride(0) if gate is not None else 0, _stream()), "b200_batched_linear")
+    return out
+
+
+def moe_experts(h, topk_weight, align, w_gate_up, w_down, top: int, limit: float = 0.0, act: int = ACT_SWISH_CLAMPED,
+                scale_input: bool = True):
+    """Routed experts: for every (token, choice) pair  W_down glu(W_gate_up (weight * h)) (scale_input), or the unweighted
+    expert output (the caller then weighs the outputs).  h [T, W]; w_gate_up [E, 2 ff, W] (gate rows first), w_down
+    [E, W, ff]; returns fp32 [T * top, W] in pair order."""
     _cuda(h, topk_weight, w_gate_up, w_down)
     sorted_ids, tile_expert, num_tiles, bm = align
     e, ff2, width = w_gate_up.shape
     ff = ff2 // 2
     tiles = tile_expert.numel()
-    act = torch.empty((sorted_ids.numel(), ff), dtype=h.dtype, device=h.device)
+    hid = torch.empty((sorted_ids.numel(), ff), dtype=h.dtype, device=h.device)
     out = torch.empty((h.shape[0] * top, width), dtype=torch.float32, device=h.device)
     lib = _cabi.load()
     if bm > moe_tile_rows():  # prompt-sized: gather and scale the pairs once, then plain rows into the pipelined kernel
         rows = torch.empty((sorted_ids.numel(), width), dtype=h.dtype, device=h.device)
         with _k("moe_gather_scale"):
-            check(lib.b200_moe_gather_scale(_ptr(h), h.stride(0), _ptr(sorted_ids), sorted_ids.numel(), top, _ptr(topk_weight),
+            check(lib.b200_moe_gather_scale(_ptr(h), h.stride(0), _ptr(sorted_ids), sorted_ids.numel(), top,
+                                            _ptr(topk_weight) if scale_input else 0,
                                             _ptr(num_tiles), bm, _ptr(rows), width, _stream()), "b200_moe_gather_scale")
         a, lda, gdiv, scale = rows, width, 0, 0
     else:
-        a, lda, gdiv, scale = h, h.stride(0), top, _ptr(topk_weight)
+        a, lda, gdiv, scale = h, h.stride(0), top, _ptr(topk_weight) if scale_input else 0
     with _k("moe_gate_up_glu"):
         check(lib.b200_grouped_linear(_ptr(a), lda, _ptr(sorted_ids), gdiv, scale, _ptr(w_gate_up), ff2 * width,
-                                      _ptr(tile_expert), _ptr(num_tiles), tiles, 0, ff, width, _edt(h), _ptr(act), ff, 0, 1,
-                                      float(limit), bm, _stream()), "b200_grouped_linear")
+                                      _ptr(tile_expert), _ptr(num_tiles), tiles, 0, ff, width, _edt(h), _ptr(hid), ff, 0, 1,
+                                      int(act), float(limit), bm, _stream()), "b200_grouped_linear")
     with _k("moe_down"):
-        check(lib.b200_grouped_linear(_ptr(act), ff, _ptr(sorted_ids), 0, 0, _ptr(w_down), width * ff, _ptr(tile_expert),
-                                      _ptr(num_tiles), tiles, 0, width, ff, _edt(h), _ptr(out), width, 1, 0, 0.0, bm, _stream()),
+        check(lib.b200_grouped_linear(_ptr(hid), ff, _ptr(sorted_ids), 0, 0, _ptr(w_down), width * ff, _ptr(tile_expert),
+                                      _ptr(num_tiles), tiles, 0, width, ff, _edt(h), _ptr(out), width, 1, 0, 0, 0.0, bm, _stream()),
               "b200_grouped_linear")
     return out
+
+
+# ------------------------------------------------------------------ post-norm hybrid decoders (delta rule + latent attention)
+def embed_bigram(tokens, table, scale: float, meta, *, bigram=None, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0,
+                 prev_state=None, want_cast: bool = True):
+    """tokens int32 [T] -> (x fp32 [T, W], the same rows in the table's type or None).  x = table[token] * scale + bigram[row]
+    with row hashed from (previous token, token); prev_state int32 [slots] carries each sequence's last token across steps."""
+    _cuda(tokens, table, bigram, prev_state)
+    assert tokens.dtype == torch.int32 and table.is_contiguous() and (bigram is None or (bigram.is_contiguous() and bigram.dtype == table.dtype))
+    t, (v, w) = tokens.numel(), table.shape
+    out = torch.empty((t, w), dtype=torch.float32, device=table.device)
+    cast = torch.empty((t, w), dtype=table.dtype, device=table.device) if want_cast else None
+    with _k("embed_bigram"):
+        check(_cabi.load().b200_embed_bigram(_ptr(tokens), _ptr(table), _ptr(bigram), _edt(table), int(buckets), int(mul_prev),
+                                             int(mul_cur), _ptr(prev_state), _ptr(meta.tok_seq), _ptr(meta.seq_start),
+                                             _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), _ptr(cast), t, w, v, float(scale),
+                                             _stream()), "b200_embed_bigram")
+    return out, cast
+
+
+def rms_residual(x, y, w, eps: float, *, offset: float = 1.0, nsum: int = 1, y_weight=None, out_dtype=None):
+    """x += rmsnorm(sum of the nsum consecutive rows of y per token, weighted by y_weight [T, nsum] when given) * (offset + w);
+    returns x in out_dtype (the next GEMM's operand) or None."""
+    _cuda(x, y, w, y_weight)
+    _f32(x, y, w, y_weight)
+    t, width = x.shape
+    assert y.shape == (t * nsum, width) and (y_weight is None or y_weight.numel() == t * nsum)
+    cast = torch.empty((t, width), dtype=out_dtype, device=x.device) if out_dtype is not None else None
+    with _k("rms_residual"):
+        check(_cabi.load().b200_rms_residual(_ptr(x), _ptr(y), nsum, _ptr(y_weight), _ptr(w), float(offset), float(eps), _ptr(cast),
+                                             _edt(out_dtype) if out_dtype is not None else F32, t, width, _stream()), "b200_rms_residual")
+    return cast
+
+
+def rmsnorm_cols(src, col0: int, n: int, w, eps: float, out_dtype, *, offset: float = 0.0):
+    """RMS norm of columns [col0, col0 + n) of the fp32 rows src, times (offset + w) -> [T, n] in out_dtype."""
+    _cuda(src, w)
+    _f32(w)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and w.numel() == n
+    t = src.shape[0]
+    out = torch.empty((t, n), dtype=out_dtype, device=src.device)
+    with _k("rmsnorm_cols"):
+        check(_cabi.load().b200_rmsnorm_cols(_ptr(src), src.stride(0), col0, n, _ptr(w), float(offset), float(eps), _ptr(out),
+                                             _edt(out), n, t, _stream()), "b200_rmsnorm_cols")
+    return out
+
+
+def head_rmsnorm_gate(o, gate_src, gate_col0: int, w, eps: float, heads: int, out_dtype):
+    """o fp32 [T, H * P]: per head o / rms(o) * w [P] * silu(gate), gate = columns gate_col0.. of the fp32 rows gate_src."""
+    _cuda(o, gate_src, w)
+    _f32(o, w)
+    assert gate_src.dtype == torch.float32 and gate_src.stride(1) == 1
+    t, hp = o.shape
+    p = hp // heads
+    assert w.numel() == p
+    out = torch.empty((t, hp), dtype=out_dtype, device=o.device)
+    with _k("head_rmsnorm_gate"):
+        check(_cabi.load().b200_head_rmsnorm_gate(_ptr(o), _ptr(gate_src), gate_src.stride(0), gate_col0, _ptr(w), float(eps),
+                                                  _ptr(out), _edt(out), t, heads, p, _stream()), "b200_head_rmsnorm_gate")
+    return out
+
+
+def glu(gate_up, act: int, out_dtype):
+    """fp32 [T, 2 ff] (gate columns first) -> act(gate) * up in out_dtype; act = ACT_SILU | ACT_GELU_TANH."""
+    _cuda(gate_up)
+    _f32(gate_up)
+    t, ff2 = gate_up.shape
+    out = torch.empty((t, ff2 // 2), dtype=out_dtype, device=gate_up.device)
+    with _k("glu"):
+        check(_cabi.load().b200_glu(_ptr(gate_up), _ptr(out), _edt(out), t, ff2 // 2, int(act), _stream()), "b200_glu")
+    return out
+
+
+def delta_rule(qkv, proj, b_col0: int, a_col0: int, a_log, dt_bias, state, meta, heads: int, kv_heads: int, dim: int, vdim: int,
+               q_scale: float, unit_eps: float = 1e-6):
+    """Gated delta rule over a ragged batch.  qkv fp32 [T, q: G*D | k: G*D | v: H*P] (convolved; q and k are normalised IN
+    PLACE); raw beta / decay inputs are columns b_col0.. / a_col0.. of the fp32 rows proj; state fp32 [slots, H, P, D] updated
+    in place.  Returns o fp32 [T, H * P]."""
+    _cuda(qkv, proj, state)
+    _f32(qkv, a_log, dt_bias, state)
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.shape[1:] == (heads, vdim, dim)
+    assert qkv.shape[1] == 2 * kv_heads * dim + heads * vdim
+    t = qkv.shape[0]
+    bg = torch.empty((t, 2 * heads), dtype=torch.float32, device=qkv.device)
+    kq = torch.empty((t, kv_heads), dtype=torch.float32, device=qkv.device)
+    out = torch.empty((t, heads * vdim), dtype=torch.float32, device=qkv.device)
+    lib = _cabi.load()
+    with _k("delta_prep"):
+        check(lib.b200_delta_prep(_ptr(qkv), qkv.stride(0), _ptr(proj), proj.stride(0), b_col0, a_col0, _ptr(a_log), _ptr(dt_bias),
+                                  _ptr(bg), _ptr(kq), t, heads, kv_heads, dim, float(q_scale), float(unit_eps), _stream()),
+              "b200_delta_prep")
+    with _k("delta_scan"):
+        check(lib.b200_delta_scan(_ptr(qkv), qkv.stride(0), _ptr(bg), _ptr(kq), _ptr(state), _ptr(meta.seq_start),
+                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, heads, kv_heads, dim, vdim,
+                                  _stream()), "b200_delta_scan")
+    return out
+
+
+def latent_kv_write(src, col0: int, kv_rank: int, rot_dim: int, rot_n: int, norm_w, eps: float, cos, sin, meta, pool):
+    """Columns [col0, col0 + kv_rank + rot_dim) of the fp32 rows src -> pool rows [RMS-normed latent | rotated shared key part]
+    at the step's slots.  pool [num_blocks, 1, block_size, kv_rank + rot_dim]; cos / sin fp32 [positions, rot_n / 2]."""
+    _cuda(src, norm_w, cos, sin, pool)
+    _f32(norm_w, cos, sin)
+    assert src.dtype == torch.float32 and src.stride(1) == 1 and pool.is_contiguous() and pool.shape[-1] == kv_rank + rot_dim
+    with _k("latent_kv_write"):
+        check(_cabi.load().b200_latent_kv_write(_ptr(src), src.stride(0), col0, kv_rank, rot_dim, rot_n, _ptr(norm_w), float(eps),
+                                                _ptr(cos), _ptr(sin), _ptr(meta.tok_pos), _ptr(meta.slot_mapping), _ptr(pool),
+                                                _edt(pool), src.shape[0], _stream()), "b200_latent_kv_write")
+
+
+def latent_q_prep(q, heads: int, dim: int, rot_dim: int, rot_n: int, kv_rank: int, cos, sin, meta, nope_dtype):
+    """q fp32 [T, H * (dim + rot_dim)] -> (unrotated parts [T, H * dim] in nope_dtype, attention query fp32 [T, H * (kv_rank +
+    rot_dim)] whose last rot_dim columns per head hold the rotated part; the first kv_rank are left for the absorbing GEMM)."""
+    _cuda(q, cos, sin)
+    _f32(q, cos, sin)
+    t = q.shape[0]
+    nope = torch.empty((t, heads * dim), dtype=nope_dtype, device=q.device)
+    q_att = torch.empty((t, heads * (kv_rank + rot_dim)), dtype=torch.float32, device=q.device)
+    with _k("latent_q_prep"):
+        check(_cabi.load().b200_latent_q_prep(_ptr(q), q.stride(0), heads, dim, rot_dim, rot_n, kv_rank, _ptr(cos), _ptr(sin),
+                                              _ptr(meta.tok_pos), _ptr(nope), _edt(nope), _ptr(q_att), t, _stream()),
+              "b200_latent_q_prep")
+    return nope, q_att

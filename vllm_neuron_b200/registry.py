@@ -4,8 +4,9 @@ model object the runner steps.
 Two families are served:
   * dense Llama / Qwen2 decoders (`B200CausalLM`): HF config.json (`architectures`), HF tensor names; a step is one prefill
     or a batch of decodes;
-  * hybrid state-space / windowed-attention / MoE decoders (`HybridCausalLM`, architecture "Pumopel"): config.json lists the
-    layers; a step is one ragged batch.
+  * hybrid decoders (`HybridCausalLM`): config.json lists the layers; a step is one ragged batch.  "Pumopel": state-space /
+    windowed-attention mixers, Dynamic-Tanh norms, MoE; "Kenetar": delta-rule / latent-attention mixers, post-norm RMS,
+    bigram embedding, dense or MoE feed-forward.
 The reference resolves the architecture the same way -- `hf_config.architectures[0]` picks the NxDI model class
 (vllm_neuron/worker/neuronx_distributed_model_loader.py:612-660).
 """
@@ -72,6 +73,7 @@ MODEL_REGISTRY: dict[str, ModelEntry] = {
     "LlamaForCausalLM": _DENSE,
     "Qwen2ForCausalLM": _DENSE,
     "Pumopel": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
+    "Kenetar": ModelEntry("hybrid", _hybrid_config, _hybrid_weights, _hybrid_build, (torch.bfloat16, torch.float32)),
 }
 
 
