@@ -55,7 +55,7 @@ __global__ void delta_prep_kernel(float* __restrict__ qkv, int ldc, const float*
 }
 
 constexpr int DS_THREADS = 128;
-constexpr int DS_CHUNK = 16;  // tokens staged per shared-memory buffer
+constexpr int DS_CHUNK = 16;  // tokens staged per shared-memory buffer (fewer when the key rows are long: the two stages must fit)
 
 template <int N>
 __device__ __forceinline__ void cp_async_f32(uint32_t dst, const float* src) {
@@ -67,7 +67,7 @@ template <int R>
 __global__ void __launch_bounds__(DS_THREADS)
     delta_scan_kernel(const float* __restrict__ qkv, int ldc, const float* __restrict__ bg, const float* __restrict__ kq,
                       float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
-                      const int32_t* __restrict__ seq_pos0, float* __restrict__ out, int H, int G, int D, int P, int L, int vec4) {
+                      const int32_t* __restrict__ seq_pos0, float* __restrict__ out, int H, int G, int D, int P, int L, int vec4, int CH) {
   griddep_launch();
   griddep_wait();
   const int sq = blockIdx.z, h = blockIdx.y, PC = DS_THREADS / L, c0 = blockIdx.x * PC;
@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(DS_THREADS)
   const int Dp = L * R;  // padded key length: rows past D stay zero
   extern __shared__ __align__(16) float ds_sm[];
   // per stage: q [CH][Dp] | k [CH][Dp] | v [CH][PC] | beta, decay, k.q [3][CH]
-  const int stage_f = DS_CHUNK * (2 * Dp + PC + 3);
+  const int stage_f = CH * (2 * Dp + PC + 3);
   float* o_s = ds_sm + 2 * stage_f;  // [CH][PC]
   const int tid = threadIdx.x, cl = tid / L, l = tid - cl * L;
   const int col = c0 + cl;
@@ -87,8 +87,8 @@ __global__ void __launch_bounds__(DS_THREADS)
   const uint32_t sm0 = smem_u32(ds_sm);
   const int vcols = P - c0 < PC ? P - c0 : PC;
   auto issue = [&](int ck) {
-    const int i0 = ck * DS_CHUNK;
-    const int cnt = n - i0 < DS_CHUNK ? n - i0 : DS_CHUNK;
+    const int i0 = ck * CH;
+    const int cnt = n - i0 < CH ? n - i0 : CH;
     if (cnt > 0) {
       const uint32_t base = sm0 + (uint32_t)((ck & 1) * stage_f * 4);
       const float* src_q = qkv + (int64_t)(t0 + i0) * ldc + (int64_t)g * D;
@@ -99,28 +99,28 @@ __global__ void __launch_bounds__(DS_THREADS)
         for (int i = tid; i < cnt * dq; i += DS_THREADS) {
           const int r = i / dq, d = (i - r * dq) * 4;
           cp_async_f32<4>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
-          cp_async_f32<4>(base + (uint32_t)(((DS_CHUNK + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
+          cp_async_f32<4>(base + (uint32_t)(((CH + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
         }
         for (int i = tid; i < cnt * vq; i += DS_THREADS) {
           const int r = i / vq, d = (i - r * vq) * 4;
-          cp_async_f32<4>(base + (uint32_t)((2 * DS_CHUNK * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+          cp_async_f32<4>(base + (uint32_t)((2 * CH * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
         }
       } else {
         for (int i = tid; i < cnt * D; i += DS_THREADS) {
           const int r = i / D, d = i - r * D;
           cp_async_f32<1>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
-          cp_async_f32<1>(base + (uint32_t)(((DS_CHUNK + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
+          cp_async_f32<1>(base + (uint32_t)(((CH + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
         }
         for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
           const int r = i / vcols, d = i - r * vcols;
-          cp_async_f32<1>(base + (uint32_t)((2 * DS_CHUNK * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+          cp_async_f32<1>(base + (uint32_t)((2 * CH * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
         }
       }
-      const uint32_t sc = base + (uint32_t)((DS_CHUNK * (2 * Dp + PC)) * 4);
+      const uint32_t sc = base + (uint32_t)((CH * (2 * Dp + PC)) * 4);
       for (int i = tid; i < cnt; i += DS_THREADS) {
         cp_async_f32<1>(sc + (uint32_t)(i * 4), bg + (int64_t)(t0 + i0 + i) * 2 * H + h);
-        cp_async_f32<1>(sc + (uint32_t)((DS_CHUNK + i) * 4), bg + (int64_t)(t0 + i0 + i) * 2 * H + H + h);
-        cp_async_f32<1>(sc + (uint32_t)((2 * DS_CHUNK + i) * 4), kq + (int64_t)(t0 + i0 + i) * G + g);
+        cp_async_f32<1>(sc + (uint32_t)((CH + i) * 4), bg + (int64_t)(t0 + i0 + i) * 2 * H + H + h);
+        cp_async_f32<1>(sc + (uint32_t)((2 * CH + i) * 4), kq + (int64_t)(t0 + i0 + i) * G + g);
       }
     }
     cp_async_commit();  // an empty group past the end keeps the wait counts uniform
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(DS_THREADS)
     for (int r = 0; r < R; ++r)
       if (l * R + r < D) S[r] = srow[r];
   }
-  const int chunks = (n + DS_CHUNK - 1) / DS_CHUNK;
+  const int chunks = (n + CH - 1) / CH;
   issue(0);
   for (int ck = 0; ck < chunks; ++ck) {
     issue(ck + 1);
@@ -143,10 +143,10 @@ __global__ void __launch_bounds__(DS_THREADS)
     __syncthreads();  // chunk ck of every thread has landed; o_s of chunk ck - 1 has been flushed
     const float* st = ds_sm + (ck & 1) * stage_f;
     const float* qs = st + l * R;
-    const float* ks = st + DS_CHUNK * Dp + l * R;
-    const float* vs = st + 2 * DS_CHUNK * Dp + cl;
-    const float* sc = st + DS_CHUNK * (2 * Dp + PC);
-    const int cnt = n - ck * DS_CHUNK < DS_CHUNK ? n - ck * DS_CHUNK : DS_CHUNK;
+    const float* ks = st + CH * Dp + l * R;
+    const float* vs = st + 2 * CH * Dp + cl;
+    const float* sc = st + CH * (2 * Dp + PC);
+    const int cnt = n - ck * CH < CH ? n - ck * CH : CH;
     for (int c = 0; c < cnt; ++c) {
       float kr[R];
       float pk0 = 0.f, pk1 = 0.f, pq0 = 0.f, pq1 = 0.f;
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(DS_THREADS)
         pk += __shfl_xor_sync(0xffffffffu, pk, o);
         pq += __shfl_xor_sync(0xffffffffu, pq, o);
       }
-      const float beta = sc[c], gd = sc[DS_CHUNK + c], dkq = sc[2 * DS_CHUNK + c];
+      const float beta = sc[c], gd = sc[CH + c], dkq = sc[2 * CH + c];
       const float u = beta * (vs[c * PC] - gd * pk);
 #pragma unroll
       for (int r = 0; r < R; ++r) S[r] = gd * S[r] + kr[r] * u;
@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(DS_THREADS)
     __syncthreads();  // o_s complete; everyone is done with stage ck & 1 before chunk ck + 2 is copied into it
     for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
       const int r = i / vcols, d = i - r * vcols;
-      out[((int64_t)(t0 + ck * DS_CHUNK + r) * H + h) * P + c0 + d] = o_s[r * PC + d];
+      out[((int64_t)(t0 + ck * CH + r) * H + h) * P + c0 + d] = o_s[r * PC + d];
     }
   }
   cp_async_wait<0>();
@@ -216,7 +216,9 @@ int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const fl
   const int PC = DS_THREADS / L;
   const int vcols_min = P % PC ? P % PC : PC;
   const int vec4 = D % 4 == 0 && ldc % 4 == 0 && P % 4 == 0 && PC % 4 == 0 && vcols_min % 4 == 0 && !((uintptr_t)qkv & 15);
-  const size_t smem = (size_t)(2 * DS_CHUNK * (2 * L * R + PC + 3) + DS_CHUNK * PC) * 4;
+  int CH = DS_CHUNK;
+  while (CH > 1 && (size_t)(2 * CH * (2 * L * R + PC + 3) + CH * PC) * 4 > 160 * 1024) CH >>= 1;
+  const size_t smem = (size_t)(2 * CH * (2 * L * R + PC + 3) + CH * PC) * 4;
   dim3 grid((P + PC - 1) / PC, H, B);
   cudaStream_t st = (cudaStream_t)stream;
 #define DS_LAUNCH(RR)                                                                                                        \
@@ -224,7 +226,7 @@ int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const fl
     if (smem > 48 * 1024)                                                                                                    \
       B200_CUDA_OK(cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
     B200_CUDA_OK(launch_kernel(delta_scan_kernel<RR>, grid, dim3(DS_THREADS), smem, st, qkv, ldc, beta_decay, kq, state,     \
-                               seq_start, seq_slot, seq_pos0, out, H, G, D, P, L, vec4));                                   \
+                               seq_start, seq_slot, seq_pos0, out, H, G, D, P, L, vec4, CH));                                   \
   } while (0)
   if (R == 8) DS_LAUNCH(8);
   else if (R == 16) DS_LAUNCH(16);
