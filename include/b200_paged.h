@@ -409,9 +409,10 @@ int b200_delta_prep(float* qkv, int ldc, const float* proj, int ldp, int b_col0,
                     void* stream);
 /* Gated delta rule over the prepared rows: per head  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
  * state fp32 [slots][H][P][D] (read when seq_pos0 > 0, zero otherwise, updated); out fp32 [T][H][P].  Head h reads key
- * head h / (H / G).  D <= 1024. */
+ * head h / (H / G).  D <= 1024.  max_new: the longest portion of the step (picks the thread layout; any value is correct). */
 int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const float* kq, float* state, const int32_t* seq_start,
-                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int G, int D, int P, void* stream);
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int max_new, int H, int G, int D, int P,
+                    void* stream);
 /* Latent attention, cache write: columns [col0, col0 + C) of the fp32 rows `in` are RMS-normed (weight norm_w) into
  * pool[slot][0..C); the next R columns are the shared rotated key part: pairs (2i, 2i+1) of its first rot_n columns turn by
  * the token's position with cos / sin from tables [positions][rot_n / 2], the rest is copied.  pool [slots][C + R]. */
@@ -423,6 +424,12 @@ int b200_latent_kv_write(const float* in, int ld, int col0, int C, int R, int ro
 int b200_latent_q_prep(const float* q, int ldq, int H, int D, int R, int rot_n, int C, const float* cos_table,
                        const float* sin_table, const int32_t* tok_pos, void* q_nope, int nope_dtype, float* q_att, int T,
                        void* stream);
+/* Latent attention for single tokens and short portions, bf16 pools, on the tensor cores: token t (position tok_pos[t], block
+ * table row tok_row[t]) attends cache rows 0..pos; q fp32 [T][H][D] (pitch ldq), rows [D] with the values in the first Dv
+ * columns; out bf16 [T][H][Dv].  D and Dv multiples of 16, Dv <= 256, else B200_ERR_UNSUPPORTED. */
+int b200_latent_attn_decode(const float* q, int ldq, const void* pool, const int32_t* block_table, int64_t bt_stride,
+                            const int32_t* tok_row, const int32_t* tok_pos, float scale, void* out, int T, int H, int D, int Dv,
+                            int block_size, void* stream);
 
 #ifdef __cplusplus
 }

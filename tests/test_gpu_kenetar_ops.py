@@ -310,11 +310,12 @@ def _attend_latents(q_att, rows, scale, C, pos):
 
 
 @pytest.mark.parametrize("dtype,C,R,H", [(torch.float32, 24, 8, 3), (torch.bfloat16, 32, 16, 4), (torch.bfloat16, 40, 12, 2),
-                                         (torch.float32, 300, 20, 2)])
+                                         (torch.float32, 300, 20, 2), (torch.bfloat16, 256, 64, 20), (torch.bfloat16, 96, 32, 16)])
 def test_attention_over_cached_latents_finds_one_key_among_hundreds(dtype, C, R, H):
     """420 cached rows over pages of 8 in shuffled order; for each probed key position (the first token, both sides of page
     borders, far back, the query's own) the query is made to point at that key, so the output must be that row's latent --
-    a kernel that skips, repeats or misplaces one key of a page shows at once.  Prompt-sized and single-token steps."""
+    a kernel that skips, repeats or misplaces one key of a page shows at once.  Single tokens and short portions (in bf16 with
+    suitable sizes: the kernel whose tile rows are the heads), and prompt-sized portions."""
     ops = _ops()
     g = torch.Generator().manual_seed(8)
     bs, n, scale = 8, 420, 0.3
@@ -329,7 +330,7 @@ def test_attention_over_cached_latents_finds_one_key_among_hundreds(dtype, C, R,
     bt = torch.zeros(3, 64, dtype=torch.int32, device=DEV)
     bt[2, :len(pages)] = torch.tensor(pages, dtype=torch.int32, device=DEV)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    for T in (1, 40):                                            # a decoded token; a portion on the prompt kernel (bf16)
+    for T in (1, 5, 40):                                         # a decoded token; a short portion; a portion on the prompt kernel (bf16)
         pos0 = n - T
         q = torch.randn(T, H, C + R, generator=g) * 0.1
         for i in range(T):

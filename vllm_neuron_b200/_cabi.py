@@ -93,9 +93,10 @@ SIGNATURES = {
     "b200_head_rmsnorm_gate": (_i, [_p, _p, _i, _i, _p, _f, _p, _i, _i, _i, _i, _p]),
     "b200_glu": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "b200_delta_prep": (_i, [_p, _i, _p, _i, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _f, _f, _p]),
-    "b200_delta_scan": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "b200_delta_scan": (_i, [_p, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "b200_latent_kv_write": (_i, [_p, _i, _i, _i, _i, _i, _p, _f, _p, _p, _p, _p, _p, _i, _i, _p]),
     "b200_latent_q_prep": (_i, [_p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _i, _p, _i, _p]),
+    "b200_latent_attn_decode": (_i, [_p, _i, _p, _p, _i64, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p]),
 }
 
 _lib = None

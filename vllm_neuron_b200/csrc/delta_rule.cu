@@ -5,11 +5,14 @@
 //     x / sqrt(sum x^2 + unit_eps), q also times q_scale; beta = sigmoid(raw_b), g = exp(-exp(A_log) softplus(raw_a + dt_bias));
 //     k . q per key head is kept for the read-out.  Everything fp32.
 //   * delta_scan: the columns of S evolve independently (column j only needs v_j), so a CTA owns PC columns of one head of
-//     one sequence and L lanes share a column, each keeping R consecutive rows in registers.  With s_k = S^T k and
+//     one sequence and L lanes share a column, each keeping R rows in registers: groups of four consecutive rows dealt
+//     round-robin to the lanes (lane l holds rows 4 L i + 4 l .. + 3, i < R / 4), so that the lanes of a column read
+//     consecutive 16-byte pieces of the staged k and q rows (no bank conflicts) and of the state.  With s_k = S^T k and
 //     s_q = S^T q taken BEFORE the update (one pass over the registers, one shuffle tree for both),
 //         u = beta (v - g s_k),   S <- g S + k u,   o = g s_q + u (k . q)
-//     is the recurrence above, term for term.  Tokens are staged through shared memory in chunks, the next chunk's
-//     cp.async copies in flight under the current chunk's steps.  State layout [slots][H][P][D] (a column's rows are
+//     is the recurrence above, term for term.  Tokens are staged through shared memory in chunks, a ring of DS_STAGES
+//     buffers whose cp.async copies run three chunks ahead of the steps (a chunk's steps take about as long as one trip to
+//     HBM, so one chunk of lead does not hide it).  State layout [slots][H][P][D] (a column's rows are
 //     contiguous), read when the sequence continues (pos0 > 0), zero otherwise, written back at the end of the portion.
 #include <math.h>
 
@@ -55,6 +58,7 @@ __global__ void delta_prep_kernel(float* __restrict__ qkv, int ldc, const float*
 }
 
 constexpr int DS_THREADS = 128;
+constexpr int DS_STAGES = 4;
 constexpr int DS_CHUNK = 16;  // tokens staged per shared-memory buffer (fewer when the key rows are long: the two stages must fit)
 
 template <int N>
@@ -62,7 +66,7 @@ __device__ __forceinline__ void cp_async_f32(uint32_t dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(dst), "l"(src), "n"(N * 4) : "memory");
 }
 
-// grid (P / PC column chunks, H, sequences); thread = (column cl = tid / L, lane part l = tid % L), rows [l R, l R + R)
+// grid (P / PC column chunks, H, sequences); thread = (column cl = tid / L, lane part l = tid % L), rows 4 L i + 4 l + {0..3}
 template <int R>
 __global__ void __launch_bounds__(DS_THREADS)
     delta_scan_kernel(const float* __restrict__ qkv, int ldc, const float* __restrict__ bg, const float* __restrict__ kq,
@@ -78,42 +82,53 @@ __global__ void __launch_bounds__(DS_THREADS)
   extern __shared__ __align__(16) float ds_sm[];
   // per stage: q [CH][Dp] | k [CH][Dp] | v [CH][PC] | beta, decay, k.q [3][CH]
   const int stage_f = CH * (2 * Dp + PC + 3);
-  float* o_s = ds_sm + 2 * stage_f;  // [CH][PC]
+  float* o_s = ds_sm + DS_STAGES * stage_f;  // [CH][PC]
   const int tid = threadIdx.x, cl = tid / L, l = tid - cl * L;
   const int col = c0 + cl;
   const bool col_ok = col < P;
-  for (int i = tid; i < 2 * stage_f; i += DS_THREADS) ds_sm[i] = 0.f;  // the pads (rows past D, columns past P) stay zero
+  for (int i = tid; i < DS_STAGES * stage_f; i += DS_THREADS) ds_sm[i] = 0.f;  // the pads (rows past D, columns past P) stay zero
   __syncthreads();
   const uint32_t sm0 = smem_u32(ds_sm);
   const int vcols = P - c0 < PC ? P - c0 : PC;
+  // this thread's first copy of a chunk and the step to its next one (rows of dq / vq 16-byte pieces, or D / vcols floats):
+  // the divisions happen once, not per chunk
+  const int dq = vec4 ? D >> 2 : D, vq = vec4 ? vcols >> 2 : vcols;
+  const int q_r0 = tid / dq, q_d0 = tid - q_r0 * dq, q_dr = DS_THREADS / dq, q_dd = DS_THREADS - q_dr * dq;
+  const int v_r0 = vq > 0 ? tid / vq : CH, v_d0 = vq > 0 ? tid - v_r0 * vq : 0, v_dr = vq > 0 ? DS_THREADS / vq : 0,
+            v_dd = vq > 0 ? DS_THREADS - v_dr * vq : 0;
+  const float* src_q0 = qkv + (int64_t)t0 * ldc + (int64_t)g * D;
+  const float* src_v0 = qkv + (int64_t)t0 * ldc + 2 * (int64_t)G * D + (int64_t)h * P + c0;
+  const int64_t k_off = (int64_t)G * D;
   auto issue = [&](int ck) {
     const int i0 = ck * CH;
     const int cnt = n - i0 < CH ? n - i0 : CH;
     if (cnt > 0) {
-      const uint32_t base = sm0 + (uint32_t)((ck & 1) * stage_f * 4);
-      const float* src_q = qkv + (int64_t)(t0 + i0) * ldc + (int64_t)g * D;
-      const float* src_k = src_q + (int64_t)G * D;
-      const float* src_v = qkv + (int64_t)(t0 + i0) * ldc + 2 * (int64_t)G * D + (int64_t)h * P + c0;
-      if (vec4) {
-        const int dq = D >> 2, vq = vcols >> 2;
-        for (int i = tid; i < cnt * dq; i += DS_THREADS) {
-          const int r = i / dq, d = (i - r * dq) * 4;
-          cp_async_f32<4>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
-          cp_async_f32<4>(base + (uint32_t)(((CH + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
-        }
-        for (int i = tid; i < cnt * vq; i += DS_THREADS) {
-          const int r = i / vq, d = (i - r * vq) * 4;
-          cp_async_f32<4>(base + (uint32_t)((2 * CH * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
-        }
-      } else {
-        for (int i = tid; i < cnt * D; i += DS_THREADS) {
-          const int r = i / D, d = i - r * D;
+      const uint32_t base = sm0 + (uint32_t)((ck % DS_STAGES) * stage_f * 4);
+      const float* src_q = src_q0 + (int64_t)i0 * ldc;
+      const float* src_v = src_v0 + (int64_t)i0 * ldc;
+      for (int r = q_r0, d = q_d0; r < cnt;) {
+        if (vec4) {
+          cp_async_f32<4>(base + (uint32_t)((r * Dp + 4 * d) * 4), src_q + (int64_t)r * ldc + 4 * d);
+          cp_async_f32<4>(base + (uint32_t)(((CH + r) * Dp + 4 * d) * 4), src_q + k_off + (int64_t)r * ldc + 4 * d);
+        } else {
           cp_async_f32<1>(base + (uint32_t)((r * Dp + d) * 4), src_q + (int64_t)r * ldc + d);
-          cp_async_f32<1>(base + (uint32_t)(((CH + r) * Dp + d) * 4), src_k + (int64_t)r * ldc + d);
+          cp_async_f32<1>(base + (uint32_t)(((CH + r) * Dp + d) * 4), src_q + k_off + (int64_t)r * ldc + d);
         }
-        for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
-          const int r = i / vcols, d = i - r * vcols;
-          cp_async_f32<1>(base + (uint32_t)((2 * CH * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+        r += q_dr;
+        d += q_dd;
+        if (d >= dq) {
+          d -= dq;
+          ++r;
+        }
+      }
+      for (int r = v_r0, d = v_d0; r < cnt;) {
+        if (vec4) cp_async_f32<4>(base + (uint32_t)((2 * CH * Dp + r * PC + 4 * d) * 4), src_v + (int64_t)r * ldc + 4 * d);
+        else cp_async_f32<1>(base + (uint32_t)((2 * CH * Dp + r * PC + d) * 4), src_v + (int64_t)r * ldc + d);
+        r += v_dr;
+        d += v_dd;
+        if (d >= vq) {
+          d -= vq;
+          ++r;
         }
       }
       const uint32_t sc = base + (uint32_t)((CH * (2 * Dp + PC)) * 4);
@@ -127,23 +142,25 @@ __global__ void __launch_bounds__(DS_THREADS)
   };
   // ---- state
   float S[R];
-  float* srow = state + (((int64_t)seq_slot[sq] * H + h) * P + (col_ok ? col : 0)) * D + l * R;
+  float* srow = state + (((int64_t)seq_slot[sq] * H + h) * P + (col_ok ? col : 0)) * D + 4 * l;
+  const int gstep = 4 * L;  // rows between two of this lane's groups of four
 #pragma unroll
   for (int r = 0; r < R; ++r) S[r] = 0.f;
   if (seq_pos0[sq] > 0 && col_ok) {
 #pragma unroll
     for (int r = 0; r < R; ++r)
-      if (l * R + r < D) S[r] = srow[r];
+      if ((r >> 2) * gstep + 4 * l + (r & 3) < D) S[r] = srow[(r >> 2) * gstep + (r & 3)];
   }
   const int chunks = (n + CH - 1) / CH;
-  issue(0);
+#pragma unroll
+  for (int i = 0; i < DS_STAGES - 1; ++i) issue(i);
   for (int ck = 0; ck < chunks; ++ck) {
-    issue(ck + 1);
-    cp_async_wait<1>();
+    issue(ck + DS_STAGES - 1);  // into the stage chunk ck - 1 used: everyone left it at the barrier that ended that chunk
+    cp_async_wait<DS_STAGES - 1>();
     __syncthreads();  // chunk ck of every thread has landed; o_s of chunk ck - 1 has been flushed
-    const float* st = ds_sm + (ck & 1) * stage_f;
-    const float* qs = st + l * R;
-    const float* ks = st + CH * Dp + l * R;
+    const float* st = ds_sm + (ck % DS_STAGES) * stage_f;
+    const float* qs = st + 4 * l;
+    const float* ks = st + CH * Dp + 4 * l;
     const float* vs = st + 2 * CH * Dp + cl;
     const float* sc = st + CH * (2 * Dp + PC);
     const int cnt = n - ck * CH < CH ? n - ck * CH : CH;
@@ -152,8 +169,8 @@ __global__ void __launch_bounds__(DS_THREADS)
       float pk0 = 0.f, pk1 = 0.f, pq0 = 0.f, pq1 = 0.f;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(ks + c * Dp + r);
-        const float4 q4 = *reinterpret_cast<const float4*>(qs + c * Dp + r);
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + c * Dp + (r >> 2) * gstep);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + c * Dp + (r >> 2) * gstep);
         kr[r] = k4.x, kr[r + 1] = k4.y, kr[r + 2] = k4.z, kr[r + 3] = k4.w;
         pk0 += S[r] * k4.x + S[r + 2] * k4.z;
         pk1 += S[r + 1] * k4.y + S[r + 3] * k4.w;
@@ -161,9 +178,12 @@ __global__ void __launch_bounds__(DS_THREADS)
         pq1 += S[r + 1] * q4.y + S[r + 3] * q4.w;
       }
       float pk = pk0 + pk1, pq = pq0 + pq1;
-      for (int o = L >> 1; o > 0; o >>= 1) {
-        pk += __shfl_xor_sync(0xffffffffu, pk, o);
-        pq += __shfl_xor_sync(0xffffffffu, pq, o);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        if (o < L) {  // L is a power of two, the same for every thread
+          pk += __shfl_xor_sync(0xffffffffu, pk, o);
+          pq += __shfl_xor_sync(0xffffffffu, pq, o);
+        }
       }
       const float beta = sc[c], gd = sc[CH + c], dkq = sc[2 * CH + c];
       const float u = beta * (vs[c * PC] - gd * pk);
@@ -171,7 +191,7 @@ __global__ void __launch_bounds__(DS_THREADS)
       for (int r = 0; r < R; ++r) S[r] = gd * S[r] + kr[r] * u;
       if (l == 0) o_s[c * PC + cl] = gd * pq + u * dkq;
     }
-    __syncthreads();  // o_s complete; everyone is done with stage ck & 1 before chunk ck + 2 is copied into it
+    __syncthreads();  // o_s complete; everyone is done with this stage before the next iteration copies a later chunk into it
     for (int i = tid; i < cnt * vcols; i += DS_THREADS) {
       const int r = i / vcols, d = i - r * vcols;
       out[((int64_t)(t0 + ck * CH + r) * H + h) * P + c0 + d] = o_s[r * PC + d];
@@ -181,7 +201,7 @@ __global__ void __launch_bounds__(DS_THREADS)
   if (col_ok) {
 #pragma unroll
     for (int r = 0; r < R; ++r)
-      if (l * R + r < D) srow[r] = S[r];
+      if ((r >> 2) * gstep + 4 * l + (r & 3) < D) srow[(r >> 2) * gstep + (r & 3)] = S[r];
   }
 }
 
@@ -203,22 +223,26 @@ int b200_delta_prep(float* qkv, int ldc, const float* proj, int ldp, int b_col0,
 }
 
 int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const float* kq, float* state, const int32_t* seq_start,
-                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int H, int G, int D, int P, void* stream) {
+                    const int32_t* seq_slot, const int32_t* seq_pos0, float* out, int B, int max_new, int H, int G, int D, int P,
+                    void* stream) {
   B200_REQUIRE(qkv && beta_decay && kq && state && seq_start && seq_slot && seq_pos0 && out, "delta_scan: null pointer");
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "delta_scan: %d heads over %d key heads", H, G);
   B200_REQUIRE(D >= 1 && D <= 1024 && P >= 1, "delta_scan: key size %d (1..1024 supported)", D);
   if (B <= 0) return B200_OK;
-  // L lanes per column (a power of two), R rows per lane: eight rows while D <= 256
+  // L lanes per column (a power of two), R rows per lane.  Portions walk many tokens and are bound by the per-token chain:
+  // eight rows per lane (while D <= 256) keep it short.  Steps of single tokens mostly move the state: 32 rows per lane put
+  // more columns into a CTA (measured at D = 128: 0.056 ms against 0.099 ms for 64 sequences x 16 heads).
+  const int rows_target = max_new > 4 ? 8 : 32;
   int L = 1;
-  while (L < 32 && L * 8 < D) L <<= 1;
+  while (L < 32 && L * rows_target < D) L <<= 1;
   const int need = (D + L - 1) / L;
   const int R = need <= 8 ? 8 : need <= 16 ? 16 : 32;
   const int PC = DS_THREADS / L;
   const int vcols_min = P % PC ? P % PC : PC;
   const int vec4 = D % 4 == 0 && ldc % 4 == 0 && P % 4 == 0 && PC % 4 == 0 && vcols_min % 4 == 0 && !((uintptr_t)qkv & 15);
   int CH = DS_CHUNK;
-  while (CH > 1 && (size_t)(2 * CH * (2 * L * R + PC + 3) + CH * PC) * 4 > 160 * 1024) CH >>= 1;
-  const size_t smem = (size_t)(2 * CH * (2 * L * R + PC + 3) + CH * PC) * 4;
+  while (CH > 4 && (size_t)(DS_STAGES * CH * (2 * L * R + PC + 3) + CH * PC) * 4 > 160 * 1024) CH >>= 1;
+  const size_t smem = (size_t)(DS_STAGES * CH * (2 * L * R + PC + 3) + CH * PC) * 4;
   dim3 grid((P + PC - 1) / PC, H, B);
   cudaStream_t st = (cudaStream_t)stream;
 #define DS_LAUNCH(RR)                                                                                                        \

@@ -32,10 +32,12 @@ __global__ void __launch_bounds__(128)
   const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
   if (i0 >= n) return;
   extern __shared__ __align__(16) unsigned char smraw[];
-  const int ldk = D + 8, ldv = Dv + 8;
+  // values that are the leading columns of the key rows (one pool for both) are read from the key tile: no second copy
+  const bool v_alias = v_pool == k_pool;
+  const int ldk = D + 8, ldv = v_alias ? ldk : Dv + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // [64][ldk]
   __nv_bfloat16* Ks0 = Qs + PF_ROWS * ldk;                      // [PF_STAGES][32][ldk]
-  __nv_bfloat16* Vs0 = Ks0 + PF_STAGES * PF_KEYS * ldk;         // [PF_STAGES][32][ldv]
+  __nv_bfloat16* Vs0 = v_alias ? Ks0 : Ks0 + PF_STAGES * PF_KEYS * ldk;  // [PF_STAGES][32][ldv]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = h / (H / G);
   const int pos0 = seq_pos0[sq];
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(128)
   const int last_row = (n - i0 < PF_ROWS ? n - i0 : PF_ROWS) - 1;
   const int j_lo = first_pos - window + 1 > 0 ? first_pos - window + 1 : 0;
   const int j_hi = first_pos + last_row;  // inclusive
-  const int kch = D / 8, vch = Dv / 8;    // 16-byte chunks per row
+  const int kch = D / 8, vch = v_alias ? 0 : Dv / 8;  // 16-byte chunks per row
   // one tile of 32 keys (K and V rows, page by page through the block table) into stage `st`; rows past j_hi are zeros
   auto issue = [&](int j0, int st) {
     __nv_bfloat16* Kd = Ks0 + st * PF_KEYS * ldk;
@@ -203,7 +205,7 @@ int b200_swa_sink_attn_prefill(const float* q, int ldq, const void* k_pool, cons
   }
   if (B <= 0 || max_new <= 0) return B200_OK;
   dim3 grid((max_new + PF_ROWS - 1) / PF_ROWS, H, B);
-  const size_t smem = ((size_t)(PF_ROWS + PF_STAGES * PF_KEYS) * (D + 8) + (size_t)PF_STAGES * PF_KEYS * (Dv + 8)) * 2;
+  const size_t smem = ((size_t)(PF_ROWS + PF_STAGES * PF_KEYS) * (D + 8) + (v_pool == k_pool ? 0 : (size_t)PF_STAGES * PF_KEYS * (Dv + 8))) * 2;
   cudaStream_t st = (cudaStream_t)stream;
   typedef __nv_bfloat16 BT;
 #define PF_LAUNCH(M)                                                                                                          \

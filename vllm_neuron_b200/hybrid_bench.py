@@ -1,4 +1,5 @@
-"""Prefill / decode throughput of the hybrid decoder next to the dense Llama decoder at equal size (bench.py --hybrid).
+"""Prefill / decode throughput of the hybrid decoders (bench.py --hybrid): the Pumopel design next to the dense Llama decoder
+at equal size (`small`, `1b`), and the Kenetar design next to Pumopel at equal size (`kenetar-small`, `kenetar-1b`).
 
 For each size: random weights, both models in bf16 on one GPU, same width / layer count / vocabulary; the dense model's
 intermediate size equals the hybrid's ACTIVE feed-forward width (top * ff + shared ff) so a token costs about the same FLOPs.
@@ -29,6 +30,69 @@ SIZES = {
                   attn=dict(heads=16, kv_heads=4, dim=64, vdim=64, window=512),
                   moe=dict(experts=8, top=2, ff=512, shared=1024), prefill=2048, batch=32, ctx=1024),
 }
+
+
+# the post-norm design at the same width / layers / vocabulary / expert sizes: layer pattern 'd d l d' repeated, the first
+# layer with a dense feed-forward of the experts' active width
+KENETAR_MIXERS = {
+    "1b": dict(delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4),
+               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=768)),
+    "small": dict(delta=dict(heads=16, kv_heads=8, dim=64, vdim=64, conv=4),
+                  latent=dict(heads=16, dim=64, rot_dim=32, vdim=64, kv_rank=128, q_rank=384)),
+}
+
+
+def kenetar_config(name: str):
+    from .hybrid import HybridConfig
+
+    sz, mx = SIZES[name], KENETAR_MIXERS[name]
+    m, la = sz["moe"], mx["latent"]
+    moe = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["ff"]}}
+    dense = {"kind": "dense", "ff": m["top"] * m["ff"]}
+    rot = {"dims": la["rot_dim"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    lat = {"type": "latent_attention", "mlp": moe, "mixer": dict(la, scale=(la["dim"] + la["rot_dim"]) ** -0.5, rot=rot)}
+    layers = [lat if i % 4 == 2 else {"type": "delta", "mlp": dense if i == 0 else moe, "mixer": dict(mx["delta"])}
+              for i in range(sz["layers"])]
+    return HybridConfig.from_dict({"architecture": "Kenetar", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-6},
+                                   "logit_scale": 1.0, "embedding": {"scale": 1.0, "bigram": {"buckets": 8191, "mul_prev": 31,
+                                                                                             "mul_cur": 7}}, "layers": layers})
+
+
+def _kenetar_floors(name, t, keys_per_query, kv_tokens, nseq):
+    """Algorithmic (flops, bytes) per launch of the post-norm design's own kernels at `t` tokens."""
+    sz, mx = SIZES[name], KENETAR_MIXERS[name]
+    d, la, m, w = mx["delta"], mx["latent"], sz["moe"], sz["width"]
+    c = 2 * d["kv_heads"] * d["dim"] + d["heads"] * d["vdim"]
+    hp = d["heads"] * d["vdim"]
+    row = la["kv_rank"] + la["rot_dim"]
+    pairs = t * m["top"]
+    used = min(m["experts"], pairs)
+    att = (2.0 * t * la["heads"] * keys_per_query * (row + la["kv_rank"]),
+           2.0 * kv_tokens * row + t * la["heads"] * (4 * row + 2 * la["kv_rank"]))
+    return {
+        "swa_sink_attn_prefill": att, "swa_sink_attn": att, "latent_attn_decode": att,
+        "delta_scan": (8.0 * t * d["heads"] * d["dim"] * d["vdim"],
+                       t * (4 * c + 4 * hp) + 8.0 * nseq * d["heads"] * d["dim"] * d["vdim"]),
+        "delta_prep": (0.0, t * 16.0 * d["kv_heads"] * d["dim"]),
+        "moe_gate_up_glu": (4.0 * pairs * m["ff"] * w, used * 4.0 * m["ff"] * w + t * 2 * w + pairs * 2 * m["ff"]),
+        "moe_down": (2.0 * pairs * m["ff"] * w, used * 2.0 * m["ff"] * w + pairs * (2 * m["ff"] + 4 * w)),
+        "moe_gather_scale": (0.0, pairs * w * 4.0),
+        "causal_conv_silu": (0.0, t * 8.0 * c),
+        "head_rmsnorm_gate": (0.0, t * hp * 10.0),
+        "rms_residual": (0.0, t * w * (4 + 4 + 4 + 2.0)),
+        "latent_kv_write": (0.0, t * row * 6.0),
+        "latent_q_prep": (0.0, t * la["heads"] * ((la["dim"] + la["rot_dim"]) * 4 + la["dim"] * 2 + la["rot_dim"] * 4.0)),
+        "rmsnorm_cols": (0.0, t * la["q_rank"] * 6.0),
+        "glu": (0.0, t * m["top"] * m["ff"] * 10.0),
+    }
+
+
+def _batched_floor(name):
+    g = re.match(r"batched_linear\[(\d+)x(\d+)x(\d+)x(\d+)\]", name)
+    if not g:
+        return None
+    b, mm, n, k = (int(g.group(i)) for i in range(1, 5))
+    return 2.0 * b * mm * n * k, 2.0 * b * (mm * k + n * k) + 3.0 * b * mm * n
 
 
 def hybrid_config(sz: dict):
@@ -117,7 +181,7 @@ def _breakdown(fn, floors, hbm, peak):
         fn()
     out = {}
     for name, (cnt, ms) in sorted(kt.summary().items(), key=lambda kv: -kv[1][0] * kv[1][1]):
-        fb = _gemm_floor(name) or floors.get(name)
+        fb = _gemm_floor(name) or _batched_floor(name) or floors.get(name)
         row = {"launches": cnt, "ms": round(ms, 4)}
         if fb:
             floor_ms = max(fb[0] / peak, fb[1] / hbm) * 1e3
@@ -126,8 +190,41 @@ def _breakdown(fn, floors, hbm, peak):
     return out
 
 
-def run(args):
+def _time_hybrid(cfg, sz, args, floors_fn, flush, hbm, peak):
+    """Prefill and decode of one hybrid model: step times and the per-kernel table."""
     from .hybrid import HybridCausalLM, StepMeta
+
+    dev = torch.device("cuda:0")
+    s_pre, b, ctx, bs = sz["prefill"], sz["batch"], sz["ctx"], 32
+    mml = max(s_pre, ctx + 64)
+    per = -(-mml // bs)
+    nblocks = b * per + 1
+    hm = HybridCausalLM(cfg, None, num_blocks=nblocks, max_num_seqs=b, max_model_len=mml, block_size=bs, device=dev)
+    rows = {r: list(range(1 + r * per, 1 + (r + 1) * per)) for r in range(b)}
+    for r, blk in rows.items():
+        hm.block_table[r, :per] = torch.tensor(blk, dtype=torch.int32, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    ptoks = torch.randint(0, sz["vocab"], (s_pre,), generator=g, dtype=torch.int32).to(dev)
+    pmeta = StepMeta.build([(0, 0, s_pre)], rows, bs, dev)
+    last = torch.tensor([s_pre - 1], device=dev)
+    dtoks = torch.randint(0, sz["vocab"], (b,), generator=g, dtype=torch.int32).to(dev)
+    dmeta = StepMeta.build([(r, ctx, 1) for r in range(b)], rows, bs, dev)
+    drows = torch.arange(b, device=dev)
+    h_pre = lambda: hm.forward(ptoks, pmeta, last)  # noqa: E731
+    h_dec = lambda: hm.forward(dtoks, dmeta, drows)  # noqa: E731
+    ms_p = _timed(h_pre, args.steps, args.warmup, flush)
+    ms_d = _timed(h_dec, args.steps, args.warmup, flush)
+    out = {"prefill_tok_s": round(s_pre / ms_p * 1e3), "prefill_ms": round(ms_p, 3),
+           "decode_tok_s": round(b / ms_d * 1e3), "decode_ms": round(ms_d, 3),
+           "kv_bytes_per_block": hm.kv_bytes_per_block(), "state_bytes_per_slot": hm.state_bytes_per_slot(),
+           "prefill_kernels": _breakdown(h_pre, floors_fn(s_pre, True), hbm, peak),
+           "decode_kernels": _breakdown(h_dec, floors_fn(b, False), hbm, peak)}
+    del hm
+    torch.cuda.empty_cache()
+    return out, rows, nblocks, mml, ptoks, dtoks
+
+
+def run(args):
     from .model import B200CausalLM
 
     dev = torch.device("cuda:0")
@@ -136,41 +233,31 @@ def run(args):
     flush = torch.empty(192 << 20, dtype=torch.float32, device=dev)  # 768 MB > L2
     names = list(SIZES) if args.hybrid == "all" else [args.hybrid]
     for name in names:
-        sz = SIZES[name]
+        kenetar = name.startswith("kenetar-")
+        sz = SIZES[name[len("kenetar-"):] if kenetar else name]
         cfg = hybrid_config(sz)
         s_pre, b, ctx = sz["prefill"], sz["batch"], sz["ctx"]
         bs = 32
-        mml = max(s_pre, ctx + 64)
-        nblocks = b * (-(-mml // bs)) + 1
-        res = {"metric": "hybrid_vs_dense_tokens_per_s", "size": name, "dtype": "bf16", "data": "synthetic (random weights)",
+        res = {"metric": "kenetar_vs_pumopel_tokens_per_s" if kenetar else "hybrid_vs_dense_tokens_per_s", "size": name,
+               "dtype": "bf16", "data": "synthetic (random weights)",
                "roofline_peaks": {"hbm_gbs": hbm / 1e9, "bf16_tflops": peak / 1e12, "source": src},
                "config": {"width": sz["width"], "layers": sz["layers"], "prefill_tokens": s_pre, "decode_batch": b,
                           "decode_ctx": ctx, "l2": "flushed between timed steps"}}
-        # ---------------- hybrid
-        hm = HybridCausalLM(cfg, None, num_blocks=nblocks, max_num_seqs=b, max_model_len=mml, block_size=bs, device=dev)
-        per = -(-mml // bs)
-        rows = {r: list(range(1 + r * per, 1 + (r + 1) * per)) for r in range(b)}
-        for r, blk in rows.items():
-            hm.block_table[r, :per] = torch.tensor(blk, dtype=torch.int32, device=dev)
-        g = torch.Generator(device="cpu").manual_seed(0)
-        ptoks = torch.randint(0, sz["vocab"], (s_pre,), generator=g, dtype=torch.int32).to(dev)
-        pmeta = StepMeta.build([(0, 0, s_pre)], rows, bs, dev)
-        last = torch.tensor([s_pre - 1], device=dev)
-        dtoks = torch.randint(0, sz["vocab"], (b,), generator=g, dtype=torch.int32).to(dev)
-        dmeta = StepMeta.build([(r, ctx, 1) for r in range(b)], rows, bs, dev)
-        drows = torch.arange(b, device=dev)
-        h_pre = lambda: hm.forward(ptoks, pmeta, last)  # noqa: E731
-        h_dec = lambda: hm.forward(dtoks, dmeta, drows)  # noqa: E731
-        ms_p = _timed(h_pre, args.steps, args.warmup, flush)
-        ms_d = _timed(h_dec, args.steps, args.warmup, flush)
         win = sz["attn"]["window"]
-        res["hybrid"] = {
-            "prefill_tok_s": round(s_pre / ms_p * 1e3), "prefill_ms": round(ms_p, 3),
-            "decode_tok_s": round(b / ms_d * 1e3), "decode_ms": round(ms_d, 3),
-            "prefill_kernels": _breakdown(h_pre, _floors(cfg, sz, s_pre, min(win, s_pre / 2), s_pre, 1), hbm, peak),
-            "decode_kernels": _breakdown(h_dec, _floors(cfg, sz, b, min(win, ctx + 1), b * min(win, ctx + 1), b), hbm, peak)}
-        del hm
-        torch.cuda.empty_cache()
+        pum_floors = lambda t, pre: _floors(cfg, sz, t, min(win, s_pre / 2) if pre else min(win, ctx + 1),  # noqa: E731
+                                            s_pre if pre else b * min(win, ctx + 1), 1 if pre else b)
+        if kenetar:
+            short = name[len("kenetar-"):]
+            ken_floors = lambda t, pre: _kenetar_floors(short, t, s_pre / 2 if pre else ctx + 1,  # noqa: E731
+                                                        s_pre if pre else b * (ctx + 1), 1 if pre else b)
+            res["kenetar"] = _time_hybrid(kenetar_config(short), sz, args, ken_floors, flush, hbm, peak)[0]
+            res["pumopel"] = _time_hybrid(cfg, sz, args, pum_floors, flush, hbm, peak)[0]
+            res["gpu_launches"] = ops.launch_count()
+            print(json.dumps(res), flush=True)
+            continue
+        # ---------------- hybrid
+        res["hybrid"], rows, nblocks, mml, ptoks, dtoks = _time_hybrid(cfg, sz, args, pum_floors, flush, hbm, peak)
+        per = -(-mml // bs)
         # ---------------- dense decoder of equal size
         shape = dense_shape(sz)
         dm = B200CausalLM(shape, None, quant="bf16", num_blocks=nblocks, max_num_seqs=b, max_model_len=mml, block_size=bs, device=dev)

@@ -757,6 +757,14 @@ def swa_sink_attn(q_src, num_heads: int, k_pool, v_pool, block_table, meta, sink
                                                           int(window), _ptr(out), num_heads, g, d, dv, v_pitch, bs, _stream()),
                   "b200_swa_sink_attn_prefill")
         return out
+    if (latent_values and sink is None and window >= (1 << 30) and k_pool.dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0
+            and dv <= 256 and q_src.stride(0) % 2 == 0):
+        # attention over cached latents, decode-sized steps: the heads of a token are the rows of a tensor-core tile
+        with _k("latent_attn_decode"):
+            check(_cabi.load().b200_latent_attn_decode(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(block_table),
+                                                       block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos), float(scale),
+                                                       _ptr(out), t, num_heads, d, dv, bs, _stream()), "b200_latent_attn_decode")
+        return out
     with _k("swa_sink_attn"):
         check(_cabi.load().b200_swa_sink_attn(_ptr(q_src), q_src.stride(0), _ptr(k_pool), _ptr(v_pool), _edt(k_pool),
                                               _ptr(block_table), block_table.stride(0), _ptr(meta.tok_row), _ptr(meta.tok_pos),
@@ -967,7 +975,7 @@ def delta_rule(qkv, proj, b_col0: int, a_col0: int, a_log, dt_bias, state, meta,
               "b200_delta_prep")
     with _k("delta_scan"):
         check(lib.b200_delta_scan(_ptr(qkv), qkv.stride(0), _ptr(bg), _ptr(kq), _ptr(state), _ptr(meta.seq_start),
-                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, heads, kv_heads, dim, vdim,
+                                  _ptr(meta.seq_slot), _ptr(meta.seq_pos0), _ptr(out), meta.num_seqs, int(meta.max_new), heads, kv_heads, dim, vdim,
                                   _stream()), "b200_delta_scan")
     return out
 
