@@ -75,6 +75,23 @@ inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   return e;
 }
 
+// Same without the programmatic-dependent-launch attribute: the grid starts when its predecessor has drained.  For kernels
+// with few, long-running CTAs whose run time depends on an even spread over the SMs: launched early, their CTAs take
+// whatever slots the predecessor's tail leaves free and double up on some SMs.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_serial(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        Args&&... args) {
+  unify_carveout(reinterpret_cast<const void*>(kern));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e == cudaSuccess) count_launch(1);
+  return e;
+}
+
 // Same, as thread-block clusters of `cluster_x` consecutive CTAs along x (grid.x must be a multiple of it).
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,

@@ -10,7 +10,8 @@
 //     consecutive 16-byte pieces of the staged k and q rows (no bank conflicts) and of the state.  With s_k = S^T k and
 //     s_q = S^T q taken BEFORE the update (one pass over the registers, one shuffle tree for both),
 //         u = beta (v - g s_k),   S <- g S + k u,   o = g s_q + u (k . q)
-//     is the recurrence above, term for term.  Tokens are staged through shared memory in chunks, a ring of DS_STAGES
+//     is the recurrence above, term for term; the kernel takes the tokens two at a time (see the loop), which halves
+//     the number of dependent reductions.  Tokens are staged through shared memory in chunks, a ring of DS_STAGES
 //     buffers whose cp.async copies run three chunks ahead of the steps (a chunk's steps take about as long as one trip to
 //     HBM, so one chunk of lead does not hide it).  State layout [slots][H][P][D] (a column's rows are
 //     contiguous), read when the sequence continues (pos0 > 0), zero otherwise, written back at the end of the portion.
@@ -72,7 +73,6 @@ __global__ void __launch_bounds__(DS_THREADS)
     delta_scan_kernel(const float* __restrict__ qkv, int ldc, const float* __restrict__ bg, const float* __restrict__ kq,
                       float* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                       const int32_t* __restrict__ seq_pos0, float* __restrict__ out, int H, int G, int D, int P, int L, int vec4, int CH) {
-  griddep_launch();
   griddep_wait();
   const int sq = blockIdx.z, h = blockIdx.y, PC = DS_THREADS / L, c0 = blockIdx.x * PC;
   const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
@@ -164,7 +164,61 @@ __global__ void __launch_bounds__(DS_THREADS)
     const float* vs = st + 2 * CH * Dp + cl;
     const float* sc = st + CH * (2 * Dp + PC);
     const int cnt = n - ck * CH < CH ? n - ck * CH : CH;
-    for (int c = 0; c < cnt; ++c) {
+    int c = 0;
+    // ---- two tokens per round: with a = S^T k1, b = S^T k2, cq = S^T q1, d = S^T q2 and the scalars e = k1 . k2,
+    // f = k1 . q2 (all six reduced over the lanes in ONE shuffle tree),
+    //     u1 = beta1 (v1 - g1 a)                 o1 = g1 cq + u1 (k1 . q1)
+    //     u2 = beta2 (v2 - g2 (g1 b + e u1))     o2 = g2 (g1 d + f u1) + u2 (k2 . q2)
+    //     S <- g1 g2 S + (g2 u1) k1 + u2 k2
+    // which is two steps of the recurrence with half the dependent reductions.
+    for (; c + 1 < cnt; c += 2) {
+      float k1[R], k2[R];
+      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, cq0 = 0.f, cq1 = 0.f, d0 = 0.f, d1 = 0.f, e0 = 0.f, f0 = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; r += 4) {
+        const int off = c * Dp + (r >> 2) * gstep;
+        const float4 ka = *reinterpret_cast<const float4*>(ks + off);
+        const float4 qa = *reinterpret_cast<const float4*>(qs + off);
+        const float4 kb = *reinterpret_cast<const float4*>(ks + off + Dp);
+        const float4 qb = *reinterpret_cast<const float4*>(qs + off + Dp);
+        k1[r] = ka.x, k1[r + 1] = ka.y, k1[r + 2] = ka.z, k1[r + 3] = ka.w;
+        k2[r] = kb.x, k2[r + 1] = kb.y, k2[r + 2] = kb.z, k2[r + 3] = kb.w;
+        a0 += S[r] * ka.x + S[r + 2] * ka.z;
+        a1 += S[r + 1] * ka.y + S[r + 3] * ka.w;
+        b0 += S[r] * kb.x + S[r + 2] * kb.z;
+        b1 += S[r + 1] * kb.y + S[r + 3] * kb.w;
+        cq0 += S[r] * qa.x + S[r + 2] * qa.z;
+        cq1 += S[r + 1] * qa.y + S[r + 3] * qa.w;
+        d0 += S[r] * qb.x + S[r + 2] * qb.z;
+        d1 += S[r + 1] * qb.y + S[r + 3] * qb.w;
+        e0 += ka.x * kb.x + ka.y * kb.y + ka.z * kb.z + ka.w * kb.w;
+        f0 += ka.x * qb.x + ka.y * qb.y + ka.z * qb.z + ka.w * qb.w;
+      }
+      float a = a0 + a1, b = b0 + b1, cq = cq0 + cq1, d = d0 + d1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        if (o < L) {
+          a += __shfl_xor_sync(0xffffffffu, a, o);
+          b += __shfl_xor_sync(0xffffffffu, b, o);
+          cq += __shfl_xor_sync(0xffffffffu, cq, o);
+          d += __shfl_xor_sync(0xffffffffu, d, o);
+          e0 += __shfl_xor_sync(0xffffffffu, e0, o);
+          f0 += __shfl_xor_sync(0xffffffffu, f0, o);
+        }
+      }
+      const float beta1 = sc[c], g1 = sc[CH + c], kq1 = sc[2 * CH + c];
+      const float beta2 = sc[c + 1], g2 = sc[CH + c + 1], kq2 = sc[2 * CH + c + 1];
+      const float u1 = beta1 * (vs[c * PC] - g1 * a);
+      const float u2 = beta2 * (vs[(c + 1) * PC] - g2 * (g1 * b + e0 * u1));
+      const float gg = g1 * g2, w1 = g2 * u1;
+#pragma unroll
+      for (int r = 0; r < R; ++r) S[r] = gg * S[r] + k1[r] * w1 + k2[r] * u2;
+      if (l == 0) {
+        o_s[c * PC + cl] = g1 * cq + u1 * kq1;
+        o_s[(c + 1) * PC + cl] = g2 * (g1 * d + f0 * u1) + u2 * kq2;
+      }
+    }
+    if (c < cnt) {  // an odd token left
       float kr[R];
       float pk0 = 0.f, pk1 = 0.f, pq0 = 0.f, pq1 = 0.f;
 #pragma unroll
@@ -197,6 +251,8 @@ __global__ void __launch_bounds__(DS_THREADS)
       out[((int64_t)(t0 + ck * CH + r) * H + h) * P + c0 + d] = o_s[r * PC + d];
     }
   }
+  // the next kernel of the stream may take SM slots from here on: earlier, its waiting CTAs would displace this kernel's own
+  griddep_launch();
   cp_async_wait<0>();
   if (col_ok) {
 #pragma unroll
@@ -229,10 +285,10 @@ int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const fl
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0, "delta_scan: %d heads over %d key heads", H, G);
   B200_REQUIRE(D >= 1 && D <= 1024 && P >= 1, "delta_scan: key size %d (1..1024 supported)", D);
   if (B <= 0) return B200_OK;
-  // L lanes per column (a power of two), R rows per lane.  Portions walk many tokens and are bound by the per-token chain:
-  // eight rows per lane (while D <= 256) keep it short.  Steps of single tokens mostly move the state: 32 rows per lane put
-  // more columns into a CTA (measured at D = 128: 0.056 ms against 0.099 ms for 64 sequences x 16 heads).
-  const int rows_target = max_new > 4 ? 8 : 32;
+  // L lanes per column (a power of two), R rows per lane.  More rows per lane mean fewer shuffles and shared-memory reads
+  // per multiply-add but fewer warps to hide their latency.  Measured at D = 128, 16 heads: one 4096-token portion 1.38 /
+  // 0.97 / 1.27 ms at 32 / 16 / 8 rows per lane; 64 single tokens 0.057 / 0.057 / 0.099 ms (they mostly move the state).
+  const int rows_target = max_new > 4 ? 16 : 32;
   int L = 1;
   while (L < 32 && L * rows_target < D) L <<= 1;
   const int need = (D + L - 1) / L;
@@ -249,8 +305,8 @@ int b200_delta_scan(const float* qkv, int ldc, const float* beta_decay, const fl
   do {                                                                                                                       \
     if (smem > 48 * 1024)                                                                                                    \
       B200_CUDA_OK(cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-    B200_CUDA_OK(launch_kernel(delta_scan_kernel<RR>, grid, dim3(DS_THREADS), smem, st, qkv, ldc, beta_decay, kq, state,     \
-                               seq_start, seq_slot, seq_pos0, out, H, G, D, P, L, vec4, CH));                                   \
+    B200_CUDA_OK(launch_kernel_serial(delta_scan_kernel<RR>, grid, dim3(DS_THREADS), smem, st, qkv, ldc, beta_decay, kq,    \
+                                      state, seq_start, seq_slot, seq_pos0, out, H, G, D, P, L, vec4, CH));                 \
   } while (0)
   if (R == 8) DS_LAUNCH(8);
   else if (R == 16) DS_LAUNCH(16);

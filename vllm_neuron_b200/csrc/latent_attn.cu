@@ -96,7 +96,6 @@ __global__ void __launch_bounds__(256)
                               const int32_t* __restrict__ block_table, int64_t bt_stride, const int32_t* __restrict__ tok_row,
                               const int32_t* __restrict__ tok_pos, float scale, __nv_bfloat16* __restrict__ out, int H, int D,
                               int Dv, int bs) {
-  griddep_launch();
   griddep_wait();
   extern __shared__ __align__(16) unsigned char la_sm[];
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -206,6 +205,8 @@ __global__ void __launch_bounds__(256)
     }
     __syncwarp();  // every lane has read the tile before the next one is copied over it
   }
+  // the next kernel of the stream may take SM slots from here on: earlier, its waiting CTAs would displace this kernel's own
+  griddep_launch();
   // ---- merge the warps: each leaves (m, l, O) in its own buffer
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);

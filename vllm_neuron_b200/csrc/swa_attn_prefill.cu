@@ -26,7 +26,6 @@ __global__ void __launch_bounds__(128)
                             const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_slot,
                             const int32_t* __restrict__ seq_pos0, const float* __restrict__ sink, float scale, int window,
                             __nv_bfloat16* __restrict__ out, int H, int G, int D, int Dv, int bs, int v_pitch) {
-  griddep_launch();
   griddep_wait();
   const int sq = blockIdx.z, h = blockIdx.y, i0 = blockIdx.x * PF_ROWS;
   const int t0 = seq_start[sq], n = seq_start[sq + 1] - t0;
@@ -167,6 +166,8 @@ __global__ void __launch_bounds__(128)
     }
     __syncthreads();  // everyone is done with this stage before the tile after next is copied into it
   }
+  // the next kernel of the stream may take SM slots from here on: earlier, its waiting CTAs would displace this kernel's own
+  griddep_launch();
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
