@@ -285,3 +285,42 @@ def test_served_from_a_checkpoint_directory_and_layer_streams(tmp_path):
     assert len(cap) == len(c.cfgd["layers"])
     for got_x, want_x in zip(cap, streams):
         assert (got_x.double().cpu() - want_x).abs().max().item() < 1e-4 * want_x.abs().max().item()
+
+
+def test_trace_replay_command_line(tmp_path):
+    """bin/trace_run as a user runs it: a checkpoint folder, steps on standard input (two requests, portions beside single
+    tokens, a step that reports nothing, a request that ends and frees its row), logits files per step."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    c = Case(cfg_b(), "float32")
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    model_dir.mkdir()
+    with open(model_dir / "config.json", "w") as f:
+        json.dump(c.cfgd, f)
+    save_file({k: v.contiguous() for k, v in c.W.items()}, str(model_dir / "model.safetensors"))
+    a, b = c.tokens(70, 31), c.tokens(9, 32)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[33:35], "want": []}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}, {"id": "a", "tokens": a[35:36], "want": [0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[36:], "want": [0, 33]}], "end": ["a"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", "float32",
+                        "--out", str(out_dir), "--max-tokens", "192"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [ln for ln in p.stdout.splitlines() if ln.startswith("done")] == [f"done {i}" for i in range(4)]
+    ra, rb = c.ref(a), c.ref(b)
+    want = {0: [ra[0], ra[32]], 1: [rb[7]], 2: [rb[8], ra[35]], 3: [ra[36], ra[69]]}
+    for n, rows in want.items():
+        got = np.fromfile(out_dir / f"{n}.f32", dtype="<f4").reshape(len(rows), -1)
+        for g, w in zip(got, rows):
+            d = torch.from_numpy(g).double() - w
+            assert (d - d.mean()).pow(2).mean().sqrt().item() < 1e-4 * (w - w.mean()).pow(2).mean().sqrt().item()
