@@ -172,8 +172,9 @@ __global__ void __launch_bounds__(DS_THREADS)
     //     S <- g1 g2 S + (g2 u1) k1 + u2 k2
     // which is two steps of the recurrence with half the dependent reductions.
     for (; c + 1 < cnt; c += 2) {
-      float k1[R], k2[R];
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, cq0 = 0.f, cq1 = 0.f, d0 = 0.f, d1 = 0.f, e0 = 0.f, f0 = 0.f;
+      // packed fp32 pairs: rows (r, r + 1) of the state, k and q go through one fma.rn.f32x2 each
+      float2 k1[R / 2], k2[R / 2];
+      float2 a2 = make_float2(0.f, 0.f), b2 = a2, c2 = a2, d2 = a2, e2 = a2, f2 = a2;
 #pragma unroll
       for (int r = 0; r < R; r += 4) {
         const int off = c * Dp + (r >> 2) * gstep;
@@ -181,19 +182,21 @@ __global__ void __launch_bounds__(DS_THREADS)
         const float4 qa = *reinterpret_cast<const float4*>(qs + off);
         const float4 kb = *reinterpret_cast<const float4*>(ks + off + Dp);
         const float4 qb = *reinterpret_cast<const float4*>(qs + off + Dp);
-        k1[r] = ka.x, k1[r + 1] = ka.y, k1[r + 2] = ka.z, k1[r + 3] = ka.w;
-        k2[r] = kb.x, k2[r + 1] = kb.y, k2[r + 2] = kb.z, k2[r + 3] = kb.w;
-        a0 += S[r] * ka.x + S[r + 2] * ka.z;
-        a1 += S[r + 1] * ka.y + S[r + 3] * ka.w;
-        b0 += S[r] * kb.x + S[r + 2] * kb.z;
-        b1 += S[r + 1] * kb.y + S[r + 3] * kb.w;
-        cq0 += S[r] * qa.x + S[r + 2] * qa.z;
-        cq1 += S[r + 1] * qa.y + S[r + 3] * qa.w;
-        d0 += S[r] * qb.x + S[r + 2] * qb.z;
-        d1 += S[r + 1] * qb.y + S[r + 3] * qb.w;
-        e0 += ka.x * kb.x + ka.y * kb.y + ka.z * kb.z + ka.w * kb.w;
-        f0 += ka.x * qb.x + ka.y * qb.y + ka.z * qb.z + ka.w * qb.w;
+        const float2 s0 = make_float2(S[r], S[r + 1]), s1 = make_float2(S[r + 2], S[r + 3]);
+        const float2 ka0 = make_float2(ka.x, ka.y), ka1 = make_float2(ka.z, ka.w);
+        const float2 kb0 = make_float2(kb.x, kb.y), kb1 = make_float2(kb.z, kb.w);
+        const float2 qb0 = make_float2(qb.x, qb.y), qb1 = make_float2(qb.z, qb.w);
+        k1[r >> 1] = ka0, k1[(r >> 1) + 1] = ka1;
+        k2[r >> 1] = kb0, k2[(r >> 1) + 1] = kb1;
+        a2 = ffma2(s1, ka1, ffma2(s0, ka0, a2));
+        b2 = ffma2(s1, kb1, ffma2(s0, kb0, b2));
+        c2 = ffma2(s1, make_float2(qa.z, qa.w), ffma2(s0, make_float2(qa.x, qa.y), c2));
+        d2 = ffma2(s1, qb1, ffma2(s0, qb0, d2));
+        e2 = ffma2(ka1, kb1, ffma2(ka0, kb0, e2));
+        f2 = ffma2(ka1, qb1, ffma2(ka0, qb0, f2));
       }
+      float e0 = e2.x + e2.y, f0 = f2.x + f2.y;
+      const float a0 = a2.x, a1 = a2.y, b0 = b2.x, b1 = b2.y, cq0 = c2.x, cq1 = c2.y, d0 = d2.x, d1 = d2.y;
       float a = a0 + a1, b = b0 + b1, cq = cq0 + cq1, d = d0 + d1;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -211,8 +214,13 @@ __global__ void __launch_bounds__(DS_THREADS)
       const float u1 = beta1 * (vs[c * PC] - g1 * a);
       const float u2 = beta2 * (vs[(c + 1) * PC] - g2 * (g1 * b + e0 * u1));
       const float gg = g1 * g2, w1 = g2 * u1;
+      const float2 gg2 = make_float2(gg, gg), w12 = make_float2(w1, w1), u22 = make_float2(u2, u2);
 #pragma unroll
-      for (int r = 0; r < R; ++r) S[r] = gg * S[r] + k1[r] * w1 + k2[r] * u2;
+      for (int r = 0; r < R; r += 2) {
+        const float2 sn = ffma2(k2[r >> 1], u22, ffma2(k1[r >> 1], w12, fmul2(gg2, make_float2(S[r], S[r + 1]))));
+        S[r] = sn.x;
+        S[r + 1] = sn.y;
+      }
       if (l == 0) {
         o_s[c * PC + cl] = g1 * cq + u1 * kq1;
         o_s[(c + 1) * PC + cl] = g2 * (g1 * d + f0 * u1) + u2 * kq2;

@@ -94,23 +94,6 @@ __global__ void conv_state_update_kernel(const float* __restrict__ in, int ld, i
 //      + S_loc[k], S_in[0] = the slot's state (zero at position 0), and stores S_in[k] over the scratch;
 //   3. the full launch starts every segment from its S_in, writes y, and the last segment writes the slot's new state.
 // The recurrence is linear in S, so this is the sequential result up to fp32 rounding; everything stays fp32.
-// packed fp32 pairs (sm_100 fma.rn.f32x2 / mul.rn.f32x2): two IEEE fp32 operations per issue slot, each lane rounded exactly
-// like the scalar instruction
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
-      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}\n"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}\n"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
 
 constexpr int SCAN_PLANES = 32;
 constexpr int SCAN_SLICES = 8;
